@@ -1,0 +1,220 @@
+// Cache-update kernels: decode append, bulk (prefill) pack, ragged -> dense decompress.
+//
+// Layout contract (reference: src/dynakv/kernels/compressed_cache.py:7-34, 184-209):
+//   lens[a,s] = r_s,  offs[a,s] = sum_{t<s} lens[a,t],  flat[a, offs .. offs+r_s) = first r_s
+//   coefficients of token s,  ptr[a] = sum_s lens[a,s].  Payload is copied verbatim (bit-exact).
+#include "dkv_common.cuh"
+
+namespace dkv {
+
+template <typename T>
+__device__ __forceinline__ void copy_row(T* dst, const T* src, int n, int lane) {
+  for (int i = lane; i < n; i += 32) dst[i] = src[i];
+}
+
+// Validate a length against [0, max_dim] and the declared step; returns the sanitised value.
+__device__ __forceinline__ int checked_len(int len, int max_dim, int step, int32_t* status, int lane) {
+  bool bad = (len < 0) || (len > max_dim) || (step > 1 && (len % step) != 0);
+  if (bad) {
+    if (lane == 0) set_status(status, DKV_ST_BAD_LENGTH);
+    len = min(max(len, 0), max_dim);
+    if (step > 1) len -= len % step;
+  }
+  return len;
+}
+
+// One block per batch row; each warp owns one (arena, side) row at a time.
+template <typename T, bool PROJECT>
+__global__ void __launch_bounds__(512) append_decode_kernel(dkv_append_args p) {
+  const int b = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int A = p.arenas_per_batch;
+  const int pos = p.seq_lens ? p.seq_lens[b] : p.seq_pos;
+  const bool pos_ok = pos >= 0 && pos < p.seq_capacity;
+  if (!pos_ok && threadIdx.x == 0) set_status(p.status, DKV_ST_OVERFLOW);
+
+  for (int item = warp; pos_ok && item < 2 * A; item += n_warps) {
+    const int side_idx = item / A, j = item - side_idx * A;
+    const dkv_side& sd = side_idx ? p.v : p.k;
+    const int a = b * A + j;
+    const T* src = reinterpret_cast<const T*>(side_idx ? p.new_v : p.new_k) + (size_t)a * p.max_dim;
+    int len = (side_idx ? p.len_v : p.len_k)[a];
+    len = checked_len(len, p.max_dim, p.len_multiple, p.status, lane);
+    const int off = sd.ptr[a];
+    if ((int64_t)off + len > sd.flat_stride) {
+      if (lane == 0) set_status(p.status, DKV_ST_OVERFLOW);
+      continue;
+    }
+    T* dst = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride + off;
+    if (PROJECT) {
+      // coefficient r = sum_d x[d] * basis[j, r, d]  (fp32 accumulate, d ascending)
+      const T* basis = reinterpret_cast<const T*>(side_idx ? p.v_basis : p.k_basis) +
+                       (size_t)j * p.max_dim * p.max_dim;
+      for (int r = lane; r < len; r += 32) {
+        const T* row = basis + (size_t)r * p.max_dim;
+        float acc = 0.f;
+        for (int d = 0; d < p.max_dim; ++d) acc = fmaf(to_f32(src[d]), to_f32(row[d]), acc);
+        dst[r] = from_f32<T>(acc);
+      }
+    } else {
+      copy_row(dst, src, len, lane);
+    }
+    __syncwarp();
+    if (lane == 0) {
+      sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = len;
+      sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
+      sd.ptr[a] = off + len;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && p.seq_lens && pos_ok) p.seq_lens[b] = pos + 1;
+}
+
+// One block per arena row: exclusive scan of the block's lengths, then row copies.
+template <typename T>
+__global__ void __launch_bounds__(256) pack_bulk_kernel(dkv_pack_args p) {
+  __shared__ int warp_tot[8];
+  __shared__ int carry_s;
+  const int a = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = a / p.arenas_per_batch, j = a - b * p.arenas_per_batch;
+  const dkv_side& sd = p.side;
+  const int base = sd.ptr[a];
+  const int n_new = p.row_counts ? min(max(p.row_counts[b], 0), p.n_new) : p.n_new;
+  const int pos0 = p.seq_lens ? p.seq_lens[b] : p.seq_pos;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+
+  const int32_t* nl = p.new_lens + (size_t)a * p.n_new;
+  for (int s0 = 0; s0 < n_new; s0 += 256) {
+    const int s = s0 + tid;
+    int len = 0;
+    if (s < n_new) len = checked_len(nl[s], p.max_dim, p.len_multiple, p.status, 0);
+    // block-wide exclusive scan
+    int incl = len;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int wbase = 0;
+    for (int w = 0; w < warp; ++w) wbase += warp_tot[w];
+    const int carry = carry_s;
+    const int off = base + carry + wbase + incl - len;
+    if (s < n_new) {
+      const int pos = pos0 + s;
+      if (pos >= 0 && pos < p.seq_capacity) {
+        sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = len;
+        sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
+      }
+    }
+    __syncthreads();
+    if (tid == 255) carry_s = carry + wbase + incl;
+    __syncthreads();
+  }
+  const int total = carry_s;
+  const bool fits = (int64_t)base + total <= sd.flat_stride && pos0 >= 0 && pos0 + n_new <= p.seq_capacity;
+  if (!fits) {
+    if (tid == 0) set_status(p.status, DKV_ST_OVERFLOW);
+    return;  // payload and write pointer are left untouched
+  }
+  // payload: one warp per token row
+  const T* st = reinterpret_cast<const T*>(p.states) + (size_t)b * p.stride_b + (size_t)j * p.stride_j;
+  T* flat = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride;
+  for (int s = warp; s < n_new; s += 8) {
+    const int pos = pos0 + s;
+    const int len = sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s];
+    const int off = sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s];
+    copy_row(flat + off, st + (size_t)s * p.stride_s, len, lane);
+  }
+  if (tid == 0) sd.ptr[a] = base + total;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) decompress_kernel(dkv_side sd, T* dense, int n_tok, int max_dim) {
+  const int a = blockIdx.y, lane = threadIdx.x & 31;
+  const int s = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (s >= n_tok) return;
+  const int len = min(sd.lens[(size_t)a * sd.lens_stride_a + (size_t)s * sd.lens_stride_s], max_dim);
+  const int off = sd.offs[(size_t)a * sd.offs_stride_a + (size_t)s * sd.offs_stride_s];
+  const T* src = reinterpret_cast<const T*>(sd.flat) + (size_t)a * sd.flat_stride + off;
+  T* dst = dense + ((size_t)a * n_tok + s) * max_dim;
+  for (int i = lane; i < max_dim; i += 32) dst[i] = i < len ? src[i] : from_f32<T>(0.f);
+}
+
+static int check_side(const dkv_side& s, const char* what) {
+  DKV_REQUIRE(s.flat && s.lens && s.offs, DKV_E_ARG, "%s: flat/lens/offs must be non-null", what);
+  DKV_REQUIRE(s.flat_stride >= 0, DKV_E_ARG, "%s: negative flat_stride", what);
+  return DKV_OK;
+}
+
+}  // namespace dkv
+
+using namespace dkv;
+
+extern "C" int dkv_append_decode(const dkv_append_args* a) {
+  DKV_REQUIRE(a != nullptr, DKV_E_ARG, "dkv_append_decode: null args");
+  DKV_REQUIRE(a->batch >= 0 && a->arenas_per_batch >= 1 && a->max_dim >= 1 && a->max_dim <= 1024, DKV_E_ARG,
+              "dkv_append_decode: bad sizes (batch=%d arenas_per_batch=%d max_dim=%d)", a->batch,
+              a->arenas_per_batch, a->max_dim);
+  DKV_REQUIRE(a->dtype >= DKV_F32 && a->dtype <= DKV_BF16, DKV_E_ARG, "dkv_append_decode: bad dtype %d", a->dtype);
+  DKV_REQUIRE(a->new_k && a->new_v && a->len_k && a->len_v, DKV_E_ARG, "dkv_append_decode: null input");
+  DKV_REQUIRE((a->k_basis == nullptr) == (a->v_basis == nullptr), DKV_E_ARG,
+              "dkv_append_decode: give both bases or neither");
+  DKV_REQUIRE(a->len_multiple >= 1, DKV_E_ARG, "dkv_append_decode: len_multiple must be >= 1");
+  if (int rc = check_side(a->k, "dkv_append_decode k")) return rc;
+  if (int rc = check_side(a->v, "dkv_append_decode v")) return rc;
+  DKV_REQUIRE(a->k.ptr && a->v.ptr, DKV_E_ARG, "dkv_append_decode: write pointers must be non-null");
+  if (a->batch == 0) return DKV_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+  const int items = 2 * a->arenas_per_batch;
+  const int threads = 32 * (items < 16 ? items : 16);
+  const bool proj = a->k_basis != nullptr;
+#define LAUNCH(T)                                                             \
+  do {                                                                        \
+    if (proj) append_decode_kernel<T, true><<<a->batch, threads, 0, st>>>(*a); \
+    else append_decode_kernel<T, false><<<a->batch, threads, 0, st>>>(*a);    \
+  } while (0)
+  if (a->dtype == DKV_F32) LAUNCH(float);
+  else if (a->dtype == DKV_F16) LAUNCH(__half);
+  else LAUNCH(__nv_bfloat16);
+#undef LAUNCH
+  DKV_CHECK_LAUNCH();
+  return DKV_OK;
+}
+
+extern "C" int dkv_pack_bulk(const dkv_pack_args* a) {
+  DKV_REQUIRE(a != nullptr, DKV_E_ARG, "dkv_pack_bulk: null args");
+  DKV_REQUIRE(a->batch >= 0 && a->arenas_per_batch >= 1 && a->n_new >= 0 && a->max_dim >= 1 && a->max_dim <= 1024,
+              DKV_E_ARG, "dkv_pack_bulk: bad sizes");
+  DKV_REQUIRE(a->dtype >= DKV_F32 && a->dtype <= DKV_BF16, DKV_E_ARG, "dkv_pack_bulk: bad dtype %d", a->dtype);
+  DKV_REQUIRE(a->states && a->new_lens && a->side.ptr, DKV_E_ARG, "dkv_pack_bulk: null input");
+  DKV_REQUIRE(a->len_multiple >= 1, DKV_E_ARG, "dkv_pack_bulk: len_multiple must be >= 1");
+  if (int rc = check_side(a->side, "dkv_pack_bulk side")) return rc;
+  const int n_arena = a->batch * a->arenas_per_batch;
+  if (n_arena == 0 || a->n_new == 0) return DKV_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+  if (a->dtype == DKV_F32) pack_bulk_kernel<float><<<n_arena, 256, 0, st>>>(*a);
+  else pack_bulk_kernel<uint16_t><<<n_arena, 256, 0, st>>>(*a);
+  DKV_CHECK_LAUNCH();
+  return DKV_OK;
+}
+
+extern "C" int dkv_decompress(int32_t dtype, int32_t n_arena, int32_t n_tok, int32_t max_dim, const dkv_side* side,
+                              void* dense, void* stream) {
+  DKV_REQUIRE(side && dense, DKV_E_ARG, "dkv_decompress: null argument");
+  DKV_REQUIRE(n_arena >= 0 && n_tok >= 0 && max_dim >= 1, DKV_E_ARG, "dkv_decompress: bad sizes");
+  DKV_REQUIRE(n_arena <= 65535, DKV_E_LIMIT, "dkv_decompress: at most 65535 arena rows per call");
+  if (int rc = check_side(*side, "dkv_decompress side")) return rc;
+  if (n_arena == 0 || n_tok == 0) return DKV_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid((n_tok + 7) / 8, n_arena);
+  if (dtype == DKV_F32) decompress_kernel<float><<<grid, 256, 0, st>>>(*side, (float*)dense, n_tok, max_dim);
+  else if (dtype == DKV_F16) decompress_kernel<__half><<<grid, 256, 0, st>>>(*side, (__half*)dense, n_tok, max_dim);
+  else if (dtype == DKV_BF16)
+    decompress_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(*side, (__nv_bfloat16*)dense, n_tok, max_dim);
+  else DKV_REQUIRE(false, DKV_E_ARG, "dkv_decompress: bad dtype %d", dtype);
+  DKV_CHECK_LAUNCH();
+  return DKV_OK;
+}

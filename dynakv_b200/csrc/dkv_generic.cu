@@ -1,0 +1,280 @@
+// Generic (CUDA-core, fp32-accumulate) decode attention over the ragged compressed cache.
+//
+// Handles every layout the reference API can express: any element type, rank R up to 1024,
+// any integer lengths, lens/offs as strided views, joint latent rows shared by all heads or
+// per-KV-head arenas.  It is the path for fp32 inputs and for caches that do not meet the
+// alignment contract of the tensor-core path, and it implements the reference's stage-1 /
+// stage-2 operators (scores, softmax.V) with their exact conventions.
+//
+// Math (reference: src/dynakv/kernels/fused.py:28-142, two_stage.py:52-157, 211-281):
+//   k_s = x^k_s . Bk[g]            (first len_s coefficients only)
+//   k'_s = RoPE_s(k_s)              (pairs (j, j+D/2), angle = s * exp(-(2j/D) ln theta), fp32)
+//   score_s = D^-1/2 (q . k'_s)
+//   softmax over s, accumulate sum_s p_s x^v_s in latent space, project once through Bv[g].
+#include <math.h>
+
+#include "dkv_common.cuh"
+
+namespace dkv {
+
+enum { MODE_ATTN = 0, MODE_SCORES = 1, MODE_SOFTMAX_V = 2 };
+
+constexpr int GD = 128;       // head_dim
+constexpr int GTT = 32;       // tokens per tile
+constexpr int GRC = 64;       // latent coefficients staged per step
+constexpr int GTHREADS = 256;
+constexpr int GZ_TOKENS = 256;  // tokens per blockIdx.z slice in MODE_SCORES
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(GTHREADS)
+generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t sc_sb, int64_t sc_sh, float log_theta) {
+  __shared__ float q_s[GD];
+  __shared__ float k_s[GTT][GD + 1];
+  __shared__ float x_s[GTT][GRC];
+  __shared__ float sc_s[GTT], p_s[GTT];
+  __shared__ int lenk_s[GTT], offk_s[GTT], lenv_s[GTT], offv_s[GTT];
+  __shared__ float alpha_s, l_s;
+  __shared__ int rmax_s;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = p.batch_index ? p.batch_index[blockIdx.x] : blockIdx.x;
+  const int h = blockIdx.y;
+  const int A = p.arenas_per_batch, Hq = p.n_q_heads, R = p.rank;
+  const int g = h / (Hq / p.n_basis_groups);
+  const int a = b * A + (h * A) / Hq;
+  int S = p.seq_len;
+  if (p.seq_lens) S = min(S, max(p.seq_lens[b], 0));
+  int t_begin = 0, t_end = S;
+  if (MODE == MODE_SCORES) {
+    t_begin = blockIdx.z * GZ_TOKENS;
+    t_end = min(p.seq_len, t_begin + GZ_TOKENS);  // scores are written for every column
+  }
+
+  const T* kflat = reinterpret_cast<const T*>(p.k.flat) + (size_t)a * p.k.flat_stride;
+  const T* vflat = reinterpret_cast<const T*>(p.v.flat) + (size_t)a * p.v.flat_stride;
+  const T* kup = reinterpret_cast<const T*>(p.k_up) + (size_t)g * R * GD;
+  const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * GD;
+  const float scale = rsqrtf((float)GD);
+
+  if (MODE != MODE_SOFTMAX_V && tid < GD) {
+    const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)h * p.q_stride_h;
+    q_s[tid] = to_f32(qp[tid]);
+  }
+  float m_run = -INFINITY;
+  float acc_lat[4] = {0.f, 0.f, 0.f, 0.f};
+  if (tid == 0) l_s = 0.f;
+  const int d = tid & (GD - 1), th = tid >> 7;
+  __syncthreads();
+
+  for (int t0 = t_begin; t0 < t_end; t0 += GTT) {
+    // ---- token metadata ----
+    if (tid < GTT) {
+      const int s = t0 + tid;
+      const bool in = s < t_end;
+      int lk = 0, ok = 0, lv = 0, ov = 0;
+      if (in) {
+        if (MODE != MODE_SOFTMAX_V) {
+          lk = p.k.lens[(size_t)a * p.k.lens_stride_a + (size_t)s * p.k.lens_stride_s];
+          ok = p.k.offs[(size_t)a * p.k.offs_stride_a + (size_t)s * p.k.offs_stride_s];
+          lk = min(max(lk, 0), R);
+        }
+        if (MODE != MODE_SCORES) {
+          lv = p.v.lens[(size_t)a * p.v.lens_stride_a + (size_t)s * p.v.lens_stride_s];
+          ov = p.v.offs[(size_t)a * p.v.offs_stride_a + (size_t)s * p.v.offs_stride_s];
+          lv = min(max(lv, 0), R);
+        }
+      }
+      lenk_s[tid] = lk; offk_s[tid] = ok; lenv_s[tid] = lv; offv_s[tid] = ov;
+      int mx = lk;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (tid == 0) rmax_s = mx;
+    }
+    __syncthreads();
+
+    if (MODE != MODE_SOFTMAX_V) {
+      // ---- K reconstruction: k[t][d] = sum_r x[t][r] * Bk[r][d] ----
+      float acc[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+      const int rmax = rmax_s;
+      for (int r0 = 0; r0 < rmax; r0 += GRC) {
+        for (int e = tid; e < GTT * GRC; e += GTHREADS) {
+          const int t = e / GRC, rr = e - t * GRC, r = r0 + rr;
+          x_s[t][rr] = (r < lenk_s[t]) ? to_f32(kflat[(size_t)offk_s[t] + r]) : 0.f;
+        }
+        __syncthreads();
+        const int nr = min(GRC, rmax - r0);
+        for (int rr = 0; rr < nr; ++rr) {
+          const float bv = to_f32(kup[(size_t)(r0 + rr) * GD + d]);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] = fmaf(x_s[th * 16 + i][rr], bv, acc[i]);
+        }
+        __syncthreads();
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) k_s[th * 16 + i][d] = acc[i];
+      __syncthreads();
+
+      // ---- optional RMSNorm, RoPE, q.k : one warp per token ----
+      for (int t = warp; t < GTT; t += GTHREADS / 32) {
+        const int s = t0 + t;
+        float k0a = k_s[t][lane], k0b = k_s[t][lane + 32];            // dims j = lane, lane+32
+        float k1a = k_s[t][lane + 64], k1b = k_s[t][lane + 96];       // dims j + 64
+        if (p.k_norm_weight) {
+          float ss = warp_sum(k0a * k0a + k0b * k0b + k1a * k1a + k1b * k1b);
+          const float rs = rsqrtf(ss * (1.0f / GD) + p.k_norm_eps);
+          k0a = p.k_norm_weight[lane] * (k0a * rs);
+          k0b = p.k_norm_weight[lane + 32] * (k0b * rs);
+          k1a = p.k_norm_weight[lane + 64] * (k1a * rs);
+          k1b = p.k_norm_weight[lane + 96] * (k1b * rs);
+        }
+        const float fa = expf(-((float)(2 * lane) / (float)GD) * log_theta);
+        const float fb = expf(-((float)(2 * (lane + 32)) / (float)GD) * log_theta);
+        float sa, ca, sb, cb;
+        sincosf((float)s * fa, &sa, &ca);
+        sincosf((float)s * fb, &sb, &cb);
+        float part = q_s[lane] * (k0a * ca - k1a * sa) + q_s[lane + 64] * (k1a * ca + k0a * sa) +
+                     q_s[lane + 32] * (k0b * cb - k1b * sb) + q_s[lane + 96] * (k1b * cb + k0b * sb);
+        part = warp_sum(part);
+        if (lane == 0) {
+          const bool in = s < t_end;
+          if (MODE == MODE_SCORES) {
+            if (in) {
+              const float v = (lenk_s[t] > 0 ? part : -1.0e4f) * scale;
+              T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)h * p.out_stride_h;
+              op[s] = from_f32<T>(v);
+            }
+          } else {
+            sc_s[t] = (in && lenk_s[t] > 0) ? part * scale : -INFINITY;
+          }
+        }
+      }
+      __syncthreads();
+    } else {
+      if (tid < GTT) {
+        const int s = t0 + tid;
+        sc_s[tid] = (s < t_end) ? to_f32(scores_in[(size_t)b * sc_sb + (size_t)h * sc_sh + s]) : -INFINITY;
+      }
+      __syncthreads();
+    }
+
+    if (MODE != MODE_SCORES) {
+      // ---- online softmax over the tile (warp 0) ----
+      if (warp == 0) {
+        const float sc = sc_s[lane];
+        const float m_new = fmaxf(m_run, warp_max(sc));
+        const float alpha = (m_new == -INFINITY) ? 1.f : __expf(m_run - m_new);
+        const float pv = (sc == -INFINITY) ? 0.f : __expf(sc - m_new);
+        const float lsum = warp_sum(pv);
+        p_s[lane] = pv;
+        if (lane == 0) { alpha_s = alpha; l_s = l_s * alpha + lsum; }
+        m_run = m_new;
+      }
+      __syncthreads();
+      // every thread tracks the running max through alpha only; warp 0 owns m_run
+      const float alpha = alpha_s;
+      // ---- latent-space V accumulation ----
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = tid + i * GTHREADS;
+        if (r < R) {
+          float accv = acc_lat[i] * alpha;
+          for (int t = 0; t < GTT; ++t) {
+            const float pv = p_s[t];
+            if (pv != 0.f && r < lenv_s[t]) accv = fmaf(pv, to_f32(vflat[(size_t)offv_s[t] + r]), accv);
+          }
+          acc_lat[i] = accv;
+        }
+      }
+      __syncthreads();
+    }
+  }
+
+  if (MODE == MODE_SCORES) return;
+
+  // ---- normalise and project the latent accumulator through Bv ----
+  float* lat_s = &k_s[0][0];  // >= 1024 floats
+  const float l = l_s;
+  float inv;
+  if (MODE == MODE_SOFTMAX_V) inv = 1.f / fmaxf(l, 1e-6f);
+  else inv = l > 0.f ? 1.f / l : 0.f;
+  if (MODE == MODE_ATTN && l <= 0.f && tid == 0) set_status(p.status, DKV_ST_EMPTY_ROW);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = tid + i * GTHREADS;
+    if (r < R) lat_s[r] = acc_lat[i] * inv;
+  }
+  __syncthreads();
+  const int r_half = (R + 1) / 2;
+  const int r_lo = th * r_half, r_hi = min(R, r_lo + r_half);
+  float o = 0.f;
+  for (int r = r_lo; r < r_hi; ++r) o = fmaf(lat_s[r], to_f32(vup[(size_t)r * GD + d]), o);
+  __syncthreads();
+  float* half_s = &x_s[0][0];  // first 128 floats of the staging tile
+  if (th == 1) half_s[d] = o;
+  __syncthreads();
+  if (th == 0) {
+    const float o1 = half_s[d];
+    T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)h * p.out_stride_h;
+    op[d] = from_f32<T>(o + o1);
+  }
+}
+
+int check_attn_args(const dkv_attn_args* a, const char* who, bool need_q, bool need_k, bool need_v) {
+  DKV_REQUIRE(a != nullptr, DKV_E_ARG, "%s: null args", who);
+  DKV_REQUIRE(a->dtype >= DKV_F32 && a->dtype <= DKV_BF16, DKV_E_ARG, "%s: bad dtype %d", who, a->dtype);
+  DKV_REQUIRE(a->head_dim == 128, DKV_E_ARG, "%s: head_dim must be 128 (got %d)", who, a->head_dim);
+  DKV_REQUIRE(a->rank >= 1 && a->rank <= 1024, DKV_E_ARG, "%s: rank must be in 1..1024 (got %d)", who, a->rank);
+  DKV_REQUIRE(a->batch >= 0 && a->seq_len >= 0, DKV_E_ARG, "%s: negative batch or seq_len", who);
+  DKV_REQUIRE(a->n_q_heads >= 1 && a->n_basis_groups >= 1 && a->n_q_heads % a->n_basis_groups == 0, DKV_E_ARG,
+              "%s: n_q_heads (%d) must be a positive multiple of n_basis_groups (%d)", who, a->n_q_heads,
+              a->n_basis_groups);
+  DKV_REQUIRE(a->arenas_per_batch >= 1 && a->n_q_heads % a->arenas_per_batch == 0, DKV_E_ARG,
+              "%s: n_q_heads (%d) must be a multiple of arenas_per_batch (%d)", who, a->n_q_heads, a->arenas_per_batch);
+  DKV_REQUIRE(a->n_q_heads <= 65535, DKV_E_LIMIT, "%s: too many heads", who);
+  DKV_REQUIRE(a->out != nullptr, DKV_E_ARG, "%s: null out", who);
+  if (need_q) DKV_REQUIRE(a->q != nullptr, DKV_E_ARG, "%s: null q", who);
+  if (need_k) DKV_REQUIRE(a->k_up && a->k.flat && a->k.lens && a->k.offs, DKV_E_ARG, "%s: null K-side input", who);
+  if (need_v) DKV_REQUIRE(a->v_up && a->v.flat && a->v.lens && a->v.offs, DKV_E_ARG, "%s: null V-side input", who);
+  return DKV_OK;
+}
+
+template <int MODE>
+static int launch_generic(const dkv_attn_args* a, const void* scores, int64_t sb, int64_t sh) {
+  if (a->batch == 0) return DKV_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+  dim3 grid(a->batch, a->n_q_heads, 1);
+  if (MODE == MODE_SCORES) {
+    if (a->seq_len == 0) return DKV_OK;
+    grid.z = (a->seq_len + GZ_TOKENS - 1) / GZ_TOKENS;
+    DKV_REQUIRE(grid.z <= 65535, DKV_E_LIMIT, "dkv_scores: seq_len too large");
+  }
+  const float log_theta = (float)log((double)a->theta);
+  if (a->dtype == DKV_F32)
+    generic_decode_kernel<float, MODE><<<grid, GTHREADS, 0, st>>>(*a, (const float*)scores, sb, sh, log_theta);
+  else if (a->dtype == DKV_F16)
+    generic_decode_kernel<__half, MODE><<<grid, GTHREADS, 0, st>>>(*a, (const __half*)scores, sb, sh, log_theta);
+  else
+    generic_decode_kernel<__nv_bfloat16, MODE><<<grid, GTHREADS, 0, st>>>(*a, (const __nv_bfloat16*)scores, sb, sh,
+                                                                        log_theta);
+  DKV_CHECK_LAUNCH();
+  return DKV_OK;
+}
+
+int generic_attention(const dkv_attn_args* a) { return launch_generic<MODE_ATTN>(a, nullptr, 0, 0); }
+
+}  // namespace dkv
+
+using namespace dkv;
+
+extern "C" int dkv_scores(const dkv_attn_args* a) {
+  if (int rc = check_attn_args(a, "dkv_scores", true, true, false)) return rc;
+  return launch_generic<MODE_SCORES>(a, nullptr, 0, 0);
+}
+
+extern "C" int dkv_softmax_v(const dkv_attn_args* a, const void* scores, int64_t sc_stride_b, int64_t sc_stride_h) {
+  if (int rc = check_attn_args(a, "dkv_softmax_v", false, false, true)) return rc;
+  DKV_REQUIRE(scores != nullptr, DKV_E_ARG, "dkv_softmax_v: null scores");
+  return launch_generic<MODE_SOFTMAX_V>(a, scores, sc_stride_b, sc_stride_h);
+}

@@ -1,0 +1,160 @@
+"""Decode-step caller of the physical path (the decode branch of the reference's attention module,
+src/dynakv/kernels/compressed_attention.py:312-357, without the model plumbing around it).
+
+``CompressedDecodeLayer.decode`` is the per-layer sequence the reference runs for every generated
+token: append the new token's truncated K/V coefficient rows to the cache, then run the routed
+compressed attention over the cache.  ``DecodeGraph`` captures that sequence for a stack of layers
+in one CUDA graph with static input/output buffers (the reference replays its gate under a graph the
+same way, compressed_attention.py:232-251), and offers ``step_from_host`` for callers whose per-step
+inputs live in host memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import _lib
+from ._common import build_attn_args, status_word
+from .compressed_cache import CustomDynamicCache
+from .router import KernelPolicy
+
+
+def merge_basis(up: torch.Tensor, n_kv_heads: int, head_dim: int, low_rank: Optional[int] = None) -> torch.Tensor:
+    """Physical basis layout of the reference's one-time merge (compressed_attention.py:278-286):
+    ``B[h, r, dd] = up[h*head_dim + dd, r]`` for a joint ``up`` of shape [n_kv_heads*head_dim, rank]."""
+    rank = up.shape[1] if low_rank is None else int(low_rank)
+    return up[:, :rank].reshape(n_kv_heads, head_dim, rank).transpose(1, 2).contiguous()
+
+
+class CompressedDecodeLayer:
+    """One attention layer's decode step on the compressed cache (per-KV-head arenas)."""
+
+    def __init__(self, layer_idx: int, k_up: torch.Tensor, v_up: torch.Tensor, theta: float,
+                 policy: Optional[KernelPolicy] = None, k_norm_weight: Optional[torch.Tensor] = None,
+                 k_norm_eps: float = 1e-6, project_new_rows: bool = False):
+        self.layer_idx = layer_idx
+        self.k_up, self.v_up = k_up.contiguous(), v_up.contiguous()
+        self.theta = float(theta)
+        self.policy = policy or KernelPolicy()
+        if k_norm_weight is not None:   # fp32 on the device once, so no conversion happens per call
+            k_norm_weight = k_norm_weight.to(device=k_up.device, dtype=torch.float32).contiguous()
+        self.k_norm_weight, self.k_norm_eps = k_norm_weight, k_norm_eps
+        self.project_new_rows = project_new_rows
+
+    def append(self, cache: CustomDynamicCache, new_k, new_v, len_k, len_v, row_counter: torch.Tensor,
+               seq_capacity: int) -> None:
+        """Append one token per arena at the position held by the device counter ``row_counter``.
+
+        new_k/new_v [B, Hkv, 128]: coefficient rows, or pre-RoPE head vectors when
+        ``project_new_rows`` (they are then projected onto the basis inside the kernel).
+        """
+        ck, cv = cache.key_cache_sp[self.layer_idx], cache.value_cache_sp[self.layer_idx]
+        a = _lib.AppendArgs()
+        a.dtype = _lib.dtype_code(new_k.dtype)
+        a.batch, a.arenas_per_batch, a.max_dim = new_k.shape[0], new_k.shape[1], new_k.shape[2]
+        a.new_k, a.new_v, a.len_k, a.len_v = new_k.data_ptr(), new_v.data_ptr(), len_k.data_ptr(), len_v.data_ptr()
+        if self.project_new_rows:
+            a.k_basis, a.v_basis = self.k_up.data_ptr(), self.v_up.data_ptr()
+        a.k, a.v = cache._side(ck), cache._side(cv)
+        a.seq_pos, a.seq_lens, a.seq_capacity = 0, row_counter.data_ptr(), seq_capacity
+        a.len_multiple = cache.len_multiple
+        a.status, a.stream = status_word(new_k.device).data_ptr(), _lib.stream_ptr(new_k.device)
+        _lib.check(_lib.load().dkv_append_decode(C.byref(a)), "dkv_append_decode")
+
+    def attend(self, cache: CustomDynamicCache, q: torch.Tensor, out: torch.Tensor, row_counter: torch.Tensor,
+               seq_columns: int, route: str, batch_index: Optional[torch.Tensor] = None,
+               prepare_only: bool = False) -> None:
+        ck, cv = cache.key_cache_sp[self.layer_idx], cache.value_cache_sp[self.layer_idx]
+        args, keep = build_attn_args(
+            q, ck[0], self.k_up, cv[0], self.v_up, ck[1][:, :seq_columns], ck[2][:, :seq_columns],
+            cv[1][:, :seq_columns], cv[2][:, :seq_columns], self.theta, out=out, seq_lens=row_counter,
+            batch_index=batch_index, k_norm_weight=self.k_norm_weight, k_norm_eps=self.k_norm_eps,
+            len_multiple=cache.len_multiple, need_workspace=(route == "long_two_stage"))
+        lib = _lib.load()
+        if prepare_only:     # only size and allocate what the call needs (workspace, status word)
+            return
+        if route == "short_fused":
+            _lib.check(lib.dkv_fused_decode(C.byref(args)), "dkv_fused_decode")
+        else:
+            _lib.check(lib.dkv_two_stage_decode(C.byref(args)), "dkv_two_stage_decode")
+        del keep
+
+
+class DecodeGraph:
+    """CUDA-graph replay of append + routed attention over a stack of layers.
+
+    The caches must have been filled (prefill) with ``token_counts`` so that every layer owns a device
+    row counter; the graph reads the current cache lengths from those counters, so one capture serves
+    every later step as long as no row crosses ``seq_capacity`` or the policy's switch point
+    (re-capture then; ``routes`` fixes which rows run which kernel).
+    """
+
+    def __init__(self, layers: Sequence[CompressedDecodeLayer], cache: CustomDynamicCache, batch: int,
+                 n_q_heads: int, dtype: torch.dtype, device, seq_lens_host: Sequence[int]):
+        self.layers, self.cache = list(layers), cache
+        self.batch, self.device = batch, torch.device(device)
+        L, Hkv = len(self.layers), cache.arenas_per_batch
+        self.q = torch.zeros((L, batch, n_q_heads, 128), dtype=dtype, device=device)
+        self.new_k = torch.zeros((L, batch, Hkv, 128), dtype=dtype, device=device)
+        self.new_v = torch.zeros_like(self.new_k)
+        self.len_k = torch.full((L, batch, Hkv), 8, dtype=torch.int32, device=device)
+        self.len_v = torch.full_like(self.len_k, 8)
+        self.out = torch.zeros((L, batch, n_q_heads, 128), dtype=dtype, device=device)
+        short, long_ = self.layers[0].policy.partition(seq_lens_host)
+        self._short = torch.tensor(short, dtype=torch.int32, device=device) if short and long_ else None
+        self._long = torch.tensor(long_, dtype=torch.int32, device=device) if short and long_ else None
+        self._has_short, self._has_long = bool(short), bool(long_)
+        self.kernel_launches_per_step = L * (1 + (1 if short else 0) + (2 if long_ else 0))
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        status_word(self.device)
+        self._run_layers(prepare_only=True)   # allocate the split workspace before any capture
+
+    def _run_layers(self, prepare_only: bool = False) -> None:
+        for li, layer in enumerate(self.layers):
+            ck = self.cache.key_cache_sp[layer.layer_idx]
+            counter = self.cache.seq_lens(layer.layer_idx)
+            if counter is None:
+                raise RuntimeError("DecodeGraph needs per-row counters: fill the cache with token_counts or adopt()")
+            cap = ck[1].shape[1]
+            if not prepare_only:
+                layer.append(self.cache, self.new_k[li], self.new_v[li], self.len_k[li], self.len_v[li], counter, cap)
+            if self._has_short:
+                layer.attend(self.cache, self.q[li], self.out[li], counter, cap, "short_fused", self._short, prepare_only)
+            if self._has_long:
+                layer.attend(self.cache, self.q[li], self.out[li], counter, cap, "long_two_stage", self._long, prepare_only)
+
+    def capture(self) -> None:
+        """Capture one decode step.  Nothing is executed: the cache is left as it is."""
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._run_layers()
+        self.graph = g
+
+    def step(self) -> torch.Tensor:
+        """Run one decode step on the static device buffers (q, new_k, new_v, len_k, len_v -> out)."""
+        if self.graph is None:
+            self._run_layers()
+        else:
+            self.graph.replay()
+        return self.out
+
+    def step_from_host(self, q, new_k, new_v, len_k, len_v, out_host: torch.Tensor) -> torch.Tensor:
+        """Host-resident step: pinned host tensors in, pinned host tensor out, copies on the current stream."""
+        self.q.copy_(q, non_blocking=True)
+        self.new_k.copy_(new_k, non_blocking=True)
+        self.new_v.copy_(new_v, non_blocking=True)
+        self.len_k.copy_(len_k, non_blocking=True)
+        self.len_v.copy_(len_v, non_blocking=True)
+        self.step()
+        out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out_host
+
+    def h2d_bytes_per_step(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.q, self.new_k, self.new_v, self.len_k, self.len_v))
+
+    def d2h_bytes_per_step(self) -> int:
+        return self.out.numel() * self.out.element_size()

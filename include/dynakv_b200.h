@@ -1,0 +1,185 @@
+/*
+ * dynakv_b200 -- C ABI of the B200 (sm_100a) compressed-KV-cache decode path.
+ *
+ * Every entry point takes plain device pointers, element strides, sizes and a
+ * CUDA stream handle; nothing here depends on torch or on C++ types.  All
+ * launches are asynchronous on `stream`; no entry point allocates or frees
+ * device memory and none synchronises, so a sequence of calls can be captured
+ * in a CUDA graph.  Return value: 0 on success, a negative DKV_E_* code when an
+ * argument was rejected on the host before any launch (dkv_last_error() then
+ * holds a message for the calling thread).  Conditions only the device can see
+ * (arena overflow, a length that breaks the declared alignment contract) are
+ * recorded in a caller-provided 32-bit status word and never trap.
+ *
+ * Each declaration names the interface of the reference project that it
+ * replaces (file:line inside the reference's source tree).
+ */
+#ifndef DYNAKV_B200_H_
+#define DYNAKV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DKV_VERSION 1
+
+/* element types of cache payload, bases, queries and outputs */
+enum { DKV_F32 = 0, DKV_F16 = 1, DKV_BF16 = 2 };
+
+/* host-side error codes */
+enum {
+  DKV_OK = 0,
+  DKV_E_ARG = -1,       /* null pointer / bad size / unsupported shape */
+  DKV_E_ALIGN = -2,     /* pointer or stride breaks a documented alignment rule */
+  DKV_E_WORKSPACE = -3, /* workspace too small */
+  DKV_E_CUDA = -4,      /* the CUDA runtime refused the launch */
+  DKV_E_LIMIT = -5      /* size beyond a fixed built-in maximum */
+};
+
+/* bits of the device status word */
+enum {
+  DKV_ST_OVERFLOW = 1,   /* an append/pack would have written past flat capacity or seq capacity; skipped */
+  DKV_ST_BAD_LENGTH = 2, /* a length was negative, above max_dim, or not a multiple of the declared step */
+  DKV_ST_EMPTY_ROW = 4   /* attention over a row with no valid token; output written as zeros */
+};
+
+/* One side (K or V) of one layer's ragged cache.
+ * Layout contract (compressed_cache.py:7-34,184-209): for arena row a and token s
+ *   lens[a,s] = kept coefficients r_s, offs[a,s] = sum_{t<s} lens[a,t] (elements),
+ *   flat[a, offs[a,s] .. +lens[a,s]) = the first r_s coefficients of the token.
+ * An "arena row" is a batch row in the reference's joint layout (arenas_per_batch = 1)
+ * or a (batch row, KV head) pair in the per-head layout (arenas_per_batch = Hkv);
+ * arena index = b * arenas_per_batch + kv_head. */
+typedef struct dkv_side {
+  void* flat;            /* [n_arena, flat_stride] elements */
+  int64_t flat_stride;   /* elements between arena rows (= capacity of a row) */
+  int32_t* lens;         /* [n_arena, seq_capacity] view */
+  int64_t lens_stride_a; /* elements between arena rows */
+  int64_t lens_stride_s; /* elements between tokens */
+  int32_t* offs;
+  int64_t offs_stride_a;
+  int64_t offs_stride_s;
+  int32_t* ptr;          /* [n_arena] write pointer = sum of lens (flat_ptr_gpu, compressed_cache.py:126) */
+} dkv_side;
+
+/* ---- decode attention -------------------------------------------------- */
+
+typedef struct dkv_attn_args {
+  int32_t dtype;            /* DKV_F32 / DKV_F16 / DKV_BF16: q, flat, bases, out */
+  int32_t batch;            /* rows processed by this call */
+  int32_t n_q_heads;        /* Hq */
+  int32_t n_basis_groups;   /* leading dim of k_up/v_up: Hkv or Hq; heads per group = Hq / groups */
+  int32_t arenas_per_batch; /* 1 (joint latent row shared by all heads) or Hkv (per-head arenas) */
+  int32_t head_dim;         /* D, must be 128 */
+  int32_t rank;             /* R = k_up.shape[1], 1..1024 */
+  int32_t seq_len;          /* S: tokens (columns of lens/offs) to attend over */
+  const void* q;            /* [*, Hq, D], already rotated; D contiguous */
+  int64_t q_stride_b, q_stride_h;
+  const void* k_up;         /* [groups, R, D] contiguous */
+  const void* v_up;
+  dkv_side k, v;
+  const int32_t* seq_lens;    /* optional [batch rows]: tokens valid per batch row (<= S); NULL = S for all */
+  const int32_t* batch_index; /* optional [batch]: which batch rows to process; NULL = 0..batch-1 */
+  const float* k_norm_weight; /* optional [D] fp32: RMSNorm of reconstructed K before RoPE (Qwen3) */
+  float k_norm_eps;
+  float theta;              /* RoPE base */
+  int32_t len_multiple;     /* caller's promise: every length is a multiple of this (1 or 8) and rows are
+                               gap-free prefix-sum packed; 8 enables the 16-byte-aligned tensor-core path */
+  void* out;                /* [*, Hq, D]; D contiguous */
+  int64_t out_stride_b, out_stride_h;
+  void* workspace;          /* scratch for the split path (see dkv_split_workspace_bytes) */
+  size_t workspace_bytes;
+  int32_t* status;          /* optional device status word (OR-ed into) */
+  int32_t n_sm;             /* SM count of the device, for grid sizing; 0 = query */
+  void* stream;             /* cudaStream_t */
+} dkv_attn_args;
+
+/* Short-cache path: one launch that reconstructs K, applies RoPE, runs QK, online softmax and V.
+ * Replaces fused_attention_dispatch (src/dynakv/kernels/fused.py:144-170). */
+int dkv_fused_decode(const dkv_attn_args* a);
+
+/* Long-cache path: split-KV partial attention into `workspace`, then a combine + V up-projection.
+ * Replaces the abx_sparse -> avx pair as the router uses it (src/dynakv/kernels/router.py:50-59,
+ * two_stage.py:159-189,283-324). dkv_two_stage_decode = dkv_split_decode then dkv_split_combine. */
+size_t dkv_split_workspace_bytes(const dkv_attn_args* a);
+int dkv_split_decode(const dkv_attn_args* a);
+int dkv_split_combine(const dkv_attn_args* a);
+int dkv_two_stage_decode(const dkv_attn_args* a);
+
+/* Stage 1 of the reference's two-stage path as a standalone op: scaled scores [batch, Hq, S] in the
+ * query dtype, tokens of length 0 get -1e4*scale. Replaces abx_sparse (two_stage.py:159-189).
+ * `out` is the score tensor; out_stride_b/out_stride_h are its strides, S contiguous. */
+int dkv_scores(const dkv_attn_args* a);
+
+/* Stage 2 as a standalone op: softmax over given scores, latent-space V accumulation, up-projection.
+ * Replaces avx (two_stage.py:283-324). scores: [batch, Hq, S] in dtype a->dtype, S contiguous. */
+int dkv_softmax_v(const dkv_attn_args* a, const void* scores, int64_t sc_stride_b, int64_t sc_stride_h);
+
+/* ---- cache update ------------------------------------------------------ */
+
+typedef struct dkv_append_args {
+  int32_t dtype;
+  int32_t batch;
+  int32_t arenas_per_batch;
+  int32_t max_dim;          /* row width of new_k/new_v per arena (R) */
+  const void* new_k;        /* [batch, arenas_per_batch, max_dim] contiguous: coefficient rows, or, when
+                               k_basis != NULL, pre-RoPE head vectors [batch, arenas_per_batch, D=max_dim] */
+  const void* new_v;
+  const int32_t* len_k;     /* [batch, arenas_per_batch] kept length r_t per new row */
+  const int32_t* len_v;
+  const void* k_basis;      /* optional [arenas_per_batch, R, D]: project the row onto the basis first */
+  const void* v_basis;
+  dkv_side k, v;
+  int32_t seq_pos;          /* token index to write when seq_lens == NULL (seq_ptr, compressed_cache.py:131) */
+  int32_t* seq_lens;        /* optional [batch]: per-row token count; written at seq_lens[b], then incremented */
+  int32_t seq_capacity;     /* columns available in lens/offs */
+  int32_t len_multiple;     /* lengths must be multiples of this, else DKV_ST_BAD_LENGTH */
+  int32_t* status;
+  void* stream;
+} dkv_append_args;
+
+/* Decode-step append of one token per arena row, K and V together, all rows in one launch.
+ * Replaces update_cache_decode_kernel and its two launches per layer
+ * (src/dynakv/kernels/compressed_cache.py:7-34,170-181,222-223). */
+int dkv_append_decode(const dkv_append_args* a);
+
+typedef struct dkv_pack_args {
+  int32_t dtype;
+  int32_t batch;
+  int32_t arenas_per_batch;
+  int32_t n_new;            /* tokens in the block */
+  int32_t max_dim;
+  const void* states;       /* element (b, j, s, i) at states[b*stride_b + j*stride_j + s*stride_s + i] */
+  int64_t stride_b, stride_j, stride_s;
+  const int32_t* new_lens;  /* [batch*arenas_per_batch, n_new] contiguous */
+  const int32_t* row_counts; /* optional [batch]: only the first row_counts[b] tokens of row b are stored */
+  const int32_t* seq_lens;  /* optional [batch]: first token index of row b (read only); NULL = seq_pos */
+  dkv_side side;
+  int32_t seq_pos;          /* first token index to write when seq_lens == NULL */
+  int32_t seq_capacity;
+  int32_t len_multiple;
+  int32_t* status;
+  void* stream;
+} dkv_pack_args;
+
+/* Bulk (prefill) pack of a block of tokens into one side: exclusive scan of the lengths, lens/offs
+ * written, kept coefficients copied back to back, write pointer advanced.
+ * Replaces the per-row python loop of _update_layer_cache (compressed_cache.py:184-209). */
+int dkv_pack_bulk(const dkv_pack_args* a);
+
+/* Ragged -> dense zero-padded [n_arena, n_tok, max_dim] (contiguous), gathered by offs.
+ * Replaces simple_decompress (compressed_cache.py:36-56). */
+int dkv_decompress(int32_t dtype, int32_t n_arena, int32_t n_tok, int32_t max_dim, const dkv_side* side,
+                   void* dense, void* stream);
+
+/* ---- misc -------------------------------------------------------------- */
+int dkv_version(void);
+const char* dkv_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DYNAKV_B200_H_ */

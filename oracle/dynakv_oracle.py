@@ -300,3 +300,26 @@ def project_rows(x: torch.Tensor, basis: torch.Tensor) -> torch.Tensor:
     (custom_attn.py:152 with the physical basis layout of
     compressed_attention.py:282).  x [N, Hkv, D], basis [Hkv, R, D] -> [N, Hkv, R] fp32."""
     return torch.einsum("nhd,hrd->nhr", x.to(torch.float32), basis.to(torch.float32))
+
+
+def compact_attention_dense(q, xk, xv, k_up, v_up, theta, valid, k_norm_weight=None, k_norm_eps=1e-6):
+    """The same compact attention as ``compact_attention`` on dense zero-masked latents, written with
+    whole-tensor torch ops the way the research model runs it (custom_attn.py:161-168 einsum
+    up-projection of the whole cache, :237-240 RoPE over 0..S-1, transformers eager attention with GQA
+    head sharing).  Used as the timed CPU baseline.
+
+    q [B,Hq,D]; xk/xv [B,Hkv,S,R]; k_up/v_up [Hkv,R,D]; valid [B,Hkv,S] bool.  Returns [B,Hq,D] fp32.
+    """
+    B, Hq, D = q.shape
+    Hkv, S = xk.shape[1], xk.shape[2]
+    G = Hq // Hkv
+    k = torch.einsum("bhsr,hrd->bhsd", xk, k_up)
+    if k_norm_weight is not None:
+        k = rms_norm(k, k_norm_weight, k_norm_eps)
+    cos, sin = rope_cos_sin(torch.arange(S), D, theta)
+    k = apply_rope(k, cos, sin)
+    v = torch.einsum("bhsr,hrd->bhsd", xv, v_up)
+    scores = torch.einsum("bhgd,bhsd->bhgs", q.view(B, Hkv, G, D), k) * (D ** -0.5)
+    scores = scores.masked_fill(~valid[:, :, None, :], float("-inf"))
+    p = torch.softmax(scores, dim=-1, dtype=torch.float32)
+    return torch.einsum("bhgs,bhsd->bhgd", p, v).reshape(B, Hq, D)

@@ -1,0 +1,85 @@
+"""CPU-only checks of the host side: router behaviour, C-ABI exports, loud failure without CUDA."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from dynakv_b200 import _lib
+from dynakv_b200.kernels.router import KernelPolicy, compressed_decode_attention
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_default_kernel_boundary():
+    policy = KernelPolicy()
+    assert policy.select(0) == "short_fused"
+    assert policy.select(499) == "short_fused"
+    assert policy.select(500) == "long_two_stage"
+
+
+def test_custom_kernel_boundary():
+    policy = KernelPolicy(switch_tokens=128)
+    assert policy.select(127) == "short_fused"
+    assert policy.select(128) == "long_two_stage"
+
+
+def test_negative_cache_length_is_rejected():
+    with pytest.raises(ValueError):
+        KernelPolicy().select(-1)
+
+
+def test_policy_is_frozen_and_partitions_rows():
+    policy = KernelPolicy()
+    with pytest.raises(Exception):
+        policy.switch_tokens = 3
+    short, long_ = policy.partition([10, 499, 500, 32768, 0])
+    assert short == [0, 1, 4] and long_ == [2, 3]
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "dynakv_b200.h")).read()
+    declared = set(re.findall(r"^(?:int|size_t|const char\*)\s+(dkv_\w+)\s*\(", header, flags=re.M))
+    assert declared, "no declarations found in the header"
+    lib = _lib.load()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/dynakv_b200.h but not exported"
+    assert declared == set(_lib.EXPORTS)
+    assert lib.dkv_version() == 1
+
+
+def test_struct_sizes_match_the_c_layout():
+    # plain C layout: natural alignment, no packing
+    assert ctypes.sizeof(_lib.Side) == 72
+    assert ctypes.sizeof(_lib.AttnArgs) % 8 == 0
+    assert _lib.AttnArgs.k.offset % 8 == 0 and _lib.AttnArgs.stream.offset % 8 == 0
+
+
+def test_host_argument_errors_need_no_gpu():
+    lib = _lib.load()
+    a = _lib.AttnArgs()
+    a.dtype, a.head_dim = 2, 64
+    assert lib.dkv_fused_decode(ctypes.byref(a)) == -1
+    assert b"head_dim" in lib.dkv_last_error()
+    assert lib.dkv_fused_decode(None) == -1
+    assert lib.dkv_split_workspace_bytes(None) == 0
+
+
+def test_operators_refuse_cpu_tensors():
+    q = torch.zeros(1, 4, 128)
+    flat = torch.zeros(1, 8)
+    lens = torch.zeros(1, 1, dtype=torch.int32)
+    up = torch.zeros(4, 8, 128)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        compressed_decode_attention(q=q, k_flat=flat, k_up=up, v_flat=flat, v_up=up, key_lengths=lens,
+                                    key_offsets=lens, value_lengths=lens, value_offsets=lens, theta=1e4,
+                                    cache_length=1)
+
+
+def test_two_stage_wrappers_require_offsets():
+    from dynakv_b200.kernels.two_stage import abx_sparse, avx
+    with pytest.raises(ValueError):
+        abx_sparse(torch.zeros(1, 4, 128), torch.zeros(4, 8, 128), torch.zeros(1, 8), torch.zeros(1, 1, dtype=torch.int32))
+    with pytest.raises(ValueError):
+        avx(torch.zeros(1, 4, 1), torch.zeros(1, 8), torch.zeros(4, 8, 128), torch.zeros(1, 1, dtype=torch.int32))

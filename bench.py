@@ -42,6 +42,8 @@ WORKLOADS = {
     "long_b8_s32768": dict(batch=8, seq=32768, dist="beta:2,8", theta=500000.0, layers=32),
     "short_b4_ragged": dict(batch=4, seq=499, dist="beta:2,5", theta=500000.0, layers=32, ragged_lo=64),
     "smoke": dict(batch=2, seq=1500, dist="beta:2,8", theta=500000.0, layers=2),
+    # small enough for a full ncu capture, still larger than L2 (2 layers x ~54 MB x 2 sequences... per layer)
+    "profile_b2_s32768": dict(batch=2, seq=32768, dist="beta:2,8", theta=500000.0, layers=3),
 }
 N_Q_HEADS, N_KV_HEADS, HEAD_DIM = 32, 8, 128
 FALLBACK_HBM_GBS = 6650.0

@@ -27,9 +27,10 @@
 namespace dkv {
 
 constexpr int D = 128;
-constexpr int NCW = 8;                 // consumer warps
+constexpr int NCW = 11;                // consumer warps (12 warps = 3 per SM sub-partition)
 constexpr int NTHREADS = (NCW + 1) * 32;
 constexpr int ST_TOK = 64;             // tokens per stage
+constexpr int GRP_PER_STAGE = ST_TOK / 16;  // 16-token groups, each handled by one consumer warp
 constexpr int NSLOT = 8;               // stages in flight (metadata slots)
 constexpr int PD = 6;                  // producer prefetch distance for lengths (stages)
 constexpr int LSTG = PD + 1;
@@ -123,13 +124,21 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
                : "r"(addr));
 }
 
+// Loads of data that does not change after the prologue barrier (the basis) carry no ordering
+// constraint, so the compiler is free to hoist and batch them.
+__device__ __forceinline__ void ldsm_x4_t_const(uint32_t (&r)[4], uint32_t addr) {
+  asm("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+      : "r"(addr));
+}
+
 template <typename T>
 struct Mma;
 template <>
 struct Mma<__nv_bfloat16> {
   static __device__ __forceinline__ void run(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -143,7 +152,7 @@ template <>
 struct Mma<__half> {
   static __device__ __forceinline__ void run(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                              uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -205,7 +214,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       sm.abort_flag = 0;
       for (int s = 0; s < NSLOT; ++s) {
         mbar_init(smem_u32(&sm.full_bar[s]), 1);
-        mbar_init(smem_u32(&sm.empty_bar[s]), NCW / 2);
+        mbar_init(smem_u32(&sm.empty_bar[s]), GRP_PER_STAGE);
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -467,15 +476,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   }
 
   // ============================= consumer warps =============================
-  const int sp = warp >> 2, gi = warp & 3;   // this warp handles stages c = sp (mod 2), token group gi
+  // 16-token groups are dealt round-robin to the consumer warps: this warp handles groups warp, warp+NCW, ...
+  // of the CTA's stage sequence (group index = stage * 4 + position in stage)
   const int gq = lane >> 2, qq = lane & 3;
   const uint32_t zero_addr = smem_u32(sm.zero_chunk);
   const uint32_t basis_lane = smem_u32(sm.basis) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * BASIS_PITCH + (lane >> 4) * 16;
   const float4* trig4 = sm.trig;
 
   int row = row0;
-  int c = sp;                 // next stage of this warp
-  // skip to the first stage >= 0 with the right parity (c already is)
+  int grp = warp;             // next group of this warp
   while (row < p.batch && sm.prefix[row] < u_end) {
     const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;   // stages of this row: [.., c_hi)
     float m_run = -INFINITY, l_part = 0.f;
@@ -483,7 +492,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 #pragma unroll
     for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
 
-    for (; c < c_hi; c += 2) {
+    for (; grp < c_hi * GRP_PER_STAGE; grp += NCW) {
+      const int c = grp / GRP_PER_STAGE, gi = grp % GRP_PER_STAGE;
       const int slot = c % NSLOT;
       if (*abort_flag) continue;
       if (!mbar_wait(smem_u32(&sm.full_bar[slot]), (uint32_t)((c / NSLOT) & 1), abort_flag)) continue;
@@ -502,18 +512,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 #pragma unroll
         for (int i = 0; i < 16; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
         const uint32_t krow = hdr.kbase + koff * 16u;
+        const int cpar16 = lane >> 4;
+        uint32_t a[4];
+        ldsm_x4(a, (cpar16 * 8 < klen) ? krow + cpar16 * 16 : zero_addr);
         for (int ks = 0; ks * 16 < kmax; ++ks) {
-          const int chunk = 2 * ks + (lane >> 4);
-          uint32_t a[4];
-          ldsm_x4(a, (chunk * 8 < klen) ? krow + chunk * 16 : zero_addr);
+          // next k-step's coefficient fragment while the tensor pipe works on this one
+          uint32_t an[4] = {0u, 0u, 0u, 0u};
+          if ((ks + 1) * 16 < kmax) {
+            const int chunk = 2 * (ks + 1) + cpar16;
+            ldsm_x4(an, (chunk * 8 < klen) ? krow + chunk * 16 : zero_addr);
+          }
+          // basis fragments are fetched four ldmatrix at a time, ahead of the eight MMAs that use them
           const uint32_t brow = basis_lane + ks * 16 * BASIS_PITCH;
 #pragma unroll
-          for (int ntp = 0; ntp < 8; ++ntp) {
-            uint32_t bb[4];
-            ldsm_x4_t(bb, brow + ntp * 32);
-            Mma<T>::run(acc[2 * ntp], a[0], a[1], a[2], a[3], bb[0], bb[1]);
-            Mma<T>::run(acc[2 * ntp + 1], a[0], a[1], a[2], a[3], bb[2], bb[3]);
+          for (int half = 0; half < 2; ++half) {
+            uint32_t bb[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ldsm_x4_t_const(bb[j], brow + (half * 4 + j) * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int ntp = half * 4 + j;
+              Mma<T>::run(acc[2 * ntp], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
+              Mma<T>::run(acc[2 * ntp + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
+            }
           }
+          a[0] = an[0]; a[1] = an[1]; a[2] = an[2]; a[3] = an[3];
         }
         // ---------------- optional RMSNorm of K (Qwen3) ----------------
         float rs0 = 1.f, rs1 = 1.f;
@@ -557,15 +580,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           // ldmatrix rows 0..3 = heads, rows 4..7 read the zero chunk
           const uint32_t qbase = smem_u32(sm.qrot[slot]);
           const int qr = lane & 7;
+          const uint32_t qaddr = (qr < HP) ? qbase + qr * Q_PITCH + (lane >> 3) * 16 : zero_addr;
+          uint32_t qa[4][4];
+#pragma unroll
+          for (int kp = 0; kp < 4; ++kp)   // {kd=2kp: d 0-7, d 8-15 ; kd=2kp+1: d 0-7, d 8-15}
+            ldsm_x4(qa[kp], (qr < HP) ? qaddr + kp * 64 : zero_addr);
 #pragma unroll
           for (int kp = 0; kp < 4; ++kp) {
-            uint32_t qa[4];
-            const uint32_t addr = (qr < HP) ? qbase + qr * Q_PITCH + (kp * 32 + (lane >> 3) * 8) * 2 : zero_addr;
-            ldsm_x4(qa, addr);   // {kd=2kp: d 0-7, d 8-15 ; kd=2kp+1: d 0-7, d 8-15}
-            Mma<T>::run(s_lo, qa[0], 0u, qa[1], 0u, kb[4 * kp][0], kb[4 * kp + 1][0]);
-            Mma<T>::run(s_hi, qa[0], 0u, qa[1], 0u, kb[4 * kp][1], kb[4 * kp + 1][1]);
-            Mma<T>::run(s_lo, qa[2], 0u, qa[3], 0u, kb[4 * kp + 2][0], kb[4 * kp + 3][0]);
-            Mma<T>::run(s_hi, qa[2], 0u, qa[3], 0u, kb[4 * kp + 2][1], kb[4 * kp + 3][1]);
+            Mma<T>::run(s_lo, qa[kp][0], 0u, qa[kp][1], 0u, kb[4 * kp][0], kb[4 * kp + 1][0]);
+            Mma<T>::run(s_hi, qa[kp][0], 0u, qa[kp][1], 0u, kb[4 * kp][1], kb[4 * kp + 1][1]);
+            Mma<T>::run(s_lo, qa[kp][2], 0u, qa[kp][3], 0u, kb[4 * kp + 2][0], kb[4 * kp + 3][0]);
+            Mma<T>::run(s_hi, qa[kp][2], 0u, qa[kp][3], 0u, kb[4 * kp + 2][1], kb[4 * kp + 3][1]);
           }
         }
         // ---------------- online softmax (base 2) ----------------
@@ -599,14 +624,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           const int vlen_t = __shfl_sync(0xffffffffu, vlen, tv);
           const uint32_t vrow = hdr.vbase + voff_t * 16u;
           const int cpar = (lane >> 3) & 1;
+          uint32_t va[8][4];
 #pragma unroll
           for (int mt = 0; mt < 8; ++mt) {
             if (mt * 16 < vmax) {
               const int chunk = 2 * mt + cpar;
-              uint32_t a[4];
-              ldsm_x4_t(a, (chunk * 8 < vlen_t) ? vrow + chunk * 16 : zero_addr);
-              Mma<T>::run(oacc[mt], a[0], a[1], a[2], a[3], pb0, pb1);
+              ldsm_x4_t(va[mt], (chunk * 8 < vlen_t) ? vrow + chunk * 16 : zero_addr);
             }
+          }
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            if (mt * 16 < vmax) Mma<T>::run(oacc[mt], va[mt][0], va[mt][1], va[mt][2], va[mt][3], pb0, pb1);
           }
         }
       }
@@ -614,7 +642,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       if (lane == 0) mbar_arrive(smem_u32(&sm.empty_bar[slot]));
     }
 
-    // ---------------- row flush: merge the 8 consumer warps ----------------
+    // ---------------- row flush: merge the consumer warps' partial states ----------------
     l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
     l_part += __shfl_xor_sync(0xffffffffu, l_part, 2);
     if (gq < HP && qq == 0) { sm.merge[warp][gq][0] = m_run; sm.merge[warp][gq][1] = l_part; }
@@ -626,12 +654,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
     consumer_bar();
     const int b = p.batch_index ? p.batch_index[row] : row;
-    const int ctid = tid;  // 0..255 over consumer threads
-    float outv[2] = {0.f, 0.f};
-    float L_tot[2] = {0.f, 0.f}, M_tot[2] = {-INFINITY, -INFINITY};
+    const int ctid = tid;  // consumer threads come first in the block
+    constexpr int N_ITEMS = HP * 128, N_IT = (N_ITEMS + NCW * 32 - 1) / (NCW * 32);
+    float outv[N_IT], L_tot[N_IT], M_tot[N_IT];
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
+    for (int it = 0; it < N_IT; ++it) {
       const int item = ctid + it * (NCW * 32);   // (head, r)
+      outv[it] = 0.f; L_tot[it] = 0.f; M_tot[it] = -INFINITY;
+      if (item >= N_ITEMS) continue;
       const int h = item >> 7, r = item & 127;
       float M = -INFINITY;
 #pragma unroll
@@ -652,8 +682,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const size_t entries_per_group = (size_t)p.batch + n_cta;
       float* rec = ws + (((size_t)g * entries_per_group + (size_t)row + blockIdx.x) * HP) * PART_STRIDE;
 #pragma unroll
-      for (int it = 0; it < 2; ++it) {
+      for (int it = 0; it < N_IT; ++it) {
         const int item = ctid + it * (NCW * 32);
+        if (item >= N_ITEMS) continue;
         const int h = item >> 7, r = item & 127;
         rec[h * PART_STRIDE + 2 + r] = outv[it];
         if (r == 0) { rec[h * PART_STRIDE] = M_tot[it]; rec[h * PART_STRIDE + 1] = L_tot[it]; }
@@ -663,8 +694,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       consumer_bar();   // all reads of merge[] done; reuse merge[0] as the normalised latent [HP][128]
       float* lat = &sm.merge[0][0][0];
 #pragma unroll
-      for (int it = 0; it < 2; ++it) {
+      for (int it = 0; it < N_IT; ++it) {
         const int item = ctid + it * (NCW * 32);
+        if (item >= N_ITEMS) continue;
         const float L = L_tot[it];
         lat[item] = L > 0.f ? outv[it] / L : 0.f;
         if (L <= 0.f && (item & 127) == 0 && (item >> 7) < G) set_status(p.status, DKV_ST_EMPTY_ROW);
@@ -672,10 +704,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       consumer_bar();
       const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * D;
 #pragma unroll
-      for (int it = 0; it < 2; ++it) {
+      for (int it = 0; it < N_IT; ++it) {
         const int item = ctid + it * (NCW * 32);
         const int h = item >> 7, d = item & 127;
-        if (h < G) {
+        if (item < N_ITEMS && h < G) {
           float o = 0.f;
           for (int r = 0; r < R; ++r) o = fmaf(lat[h * 128 + r], to_f32(vup[(size_t)r * D + d]), o);
           T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)(g * G + h) * p.out_stride_h;

@@ -214,7 +214,6 @@ def run_ours(args):
     if graph._has_long:
         from dynakv_b200.kernels._common import build_attn_args
         lib = _lib.load()
-        evs = []
         calls = []
         for li, layer in enumerate(graph.layers):
             ck, cv = cache.key_cache_sp[li], cache.value_cache_sp[li]
@@ -223,16 +222,26 @@ def run_ours(args):
                                       cv[1][:, :cap], cv[2][:, :cap], layer.theta, out=graph.out[li],
                                       seq_lens=cache.seq_lens(li), len_multiple=8, need_workspace=True)
             calls.append((a, keep))
-        for rep in range(1 + max(1, min(args.steps, 5))):
-            for a, _ in calls:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                _lib.check(lib.dkv_split_decode(C.byref(a)), "dkv_split_decode")
-                e1.record()
-                if rep > 0:
-                    evs.append((e0, e1))
+        # all layers' split launches are captured into one graph, so the events bracket back-to-back
+        # launches of this kernel only (no host gaps); duration per launch = replay time / launches
+        for a, _ in calls:   # eager warm-up (also sets the function attributes outside capture)
+            _lib.check(lib.dkv_split_decode(C.byref(a)), "dkv_split_decode")
         torch.cuda.synchronize()
-        kernel_ms = sum(a_.elapsed_time(b_) for a_, b_ in evs) / len(evs)
+        kgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(kgraph):
+            for a, _ in calls:
+                a.stream = _lib.stream_ptr(dev)
+                _lib.check(lib.dkv_split_decode(C.byref(a)), "dkv_split_decode")
+        kgraph.replay()
+        torch.cuda.synchronize()
+        reps = max(1, min(args.steps, 5))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            kgraph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        kernel_ms = e0.elapsed_time(e1) / (reps * len(calls))
     status = _common.read_status(dev)
 
     if rank != 0:

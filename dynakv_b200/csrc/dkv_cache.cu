@@ -70,6 +70,78 @@ __global__ void __launch_bounds__(512) append_decode_kernel(dkv_append_args p) {
   if (threadIdx.x == 0 && p.seq_lens && pos_ok) p.seq_lens[b] = pos + 1;
 }
 
+// Decode append with in-kernel projection (per-head layout, max_dim == head_dim == 128):
+// coefficient r = sum_d x[d] * basis[j, r, d].  One block per batch row; each (arena, side) row is
+// shared by `wpi` warps.  A warp takes 8 basis rows per iteration: lane l holds x[4l..4l+3], loads its
+// 8-byte slice of each row (coalesced 256 B per row), and the 8 dot products are reduced with
+// interleaved shuffles, so eight independent L2 loads are in flight per lane.
+template <typename T>
+__global__ void __launch_bounds__(1024) append_project_kernel(dkv_append_args p, int wpi) {
+  const int b = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int A = p.arenas_per_batch;
+  const int pos = p.seq_lens ? p.seq_lens[b] : p.seq_pos;
+  const bool pos_ok = pos >= 0 && pos < p.seq_capacity;
+  if (!pos_ok && threadIdx.x == 0) set_status(p.status, DKV_ST_OVERFLOW);
+  const int n_items = 2 * A;
+  const int warps_total = blockDim.x >> 5;
+  for (int item = warp / wpi; pos_ok && item < n_items; item += warps_total / wpi) {
+    const int sub = warp % wpi;
+    const int side_idx = item / A, j = item - side_idx * A;
+    const dkv_side& sd = side_idx ? p.v : p.k;
+    const int a = b * A + j;
+    const T* src = reinterpret_cast<const T*>(side_idx ? p.new_v : p.new_k) + (size_t)a * 128;
+    int len = (side_idx ? p.len_v : p.len_k)[a];
+    len = checked_len(len, 128, p.len_multiple, p.status, lane + sub);
+    const int off = sd.ptr[a];
+    if ((int64_t)off + len > sd.flat_stride) {
+      if (lane == 0 && sub == 0) set_status(p.status, DKV_ST_OVERFLOW);
+      continue;
+    }
+    T* dst = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride + off;
+    const T* basis = reinterpret_cast<const T*>(side_idx ? p.v_basis : p.k_basis) + (size_t)j * 128 * 128;
+    float x[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = to_f32(src[lane * 4 + e]);
+    for (int r0 = sub * 8; r0 < len; r0 += 8 * wpi) {
+      float acc[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const T* row = basis + (size_t)(r0 + u) * 128 + lane * 4;   // r0 + u < 128 always (len <= 128, step 8)
+        float s = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s = fmaf(x[e], to_f32(row[e]), s);
+        acc[u] = s;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+      }
+      if (lane < 8 && r0 + lane < len) {
+        float v = acc[0];
+#pragma unroll
+        for (int u = 1; u < 8; ++u) v = (lane == u) ? acc[u] : v;
+        dst[r0 + lane] = from_f32<T>(v);
+      }
+    }
+    if (lane == 0 && sub == 0) {
+      sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = len;
+      sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
+    }
+  }
+  __syncthreads();   // every warp has read ptr[] and seq_lens[] before they move
+  for (int item = threadIdx.x; pos_ok && item < n_items; item += blockDim.x) {
+    const int side_idx = item / A, j = item - side_idx * A;
+    const dkv_side& sd = side_idx ? p.v : p.k;
+    const int a = b * A + j;
+    const int len = sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s];
+    const int off = sd.ptr[a];
+    if ((int64_t)off + len <= sd.flat_stride) sd.ptr[a] = off + len;
+  }
+  if (threadIdx.x == 0 && p.seq_lens && pos_ok) p.seq_lens[b] = pos + 1;
+}
+
 // One block per arena row: exclusive scan of the block's lengths, then row copies.
 template <typename T>
 __global__ void __launch_bounds__(256) pack_bulk_kernel(dkv_pack_args p) {
@@ -171,9 +243,14 @@ extern "C" int dkv_append_decode(const dkv_append_args* a) {
   const int items = 2 * a->arenas_per_batch;
   const int threads = 32 * (items < 16 ? items : 16);
   const bool proj = a->k_basis != nullptr;
+  int wpi = 1;   // warps per (arena, side) row in the projecting kernel: fill a 1024-thread block
+  while (wpi * 2 * items <= 32 && wpi < 4) wpi *= 2;
+  if (proj)
+    DKV_REQUIRE(a->max_dim == 128 && a->dtype != DKV_F32 && items <= 32, DKV_E_ARG,
+                "dkv_append_decode: in-kernel projection needs 128-wide 16-bit rows and at most 16 arenas per batch row");
 #define LAUNCH(T)                                                             \
   do {                                                                        \
-    if (proj) append_decode_kernel<T, true><<<a->batch, threads, 0, st>>>(*a); \
+    if (proj) append_project_kernel<T><<<a->batch, 32 * wpi * items, 0, st>>>(*a, wpi); \
     else append_decode_kernel<T, false><<<a->batch, threads, 0, st>>>(*a);    \
   } while (0)
   if (a->dtype == DKV_F32) LAUNCH(float);

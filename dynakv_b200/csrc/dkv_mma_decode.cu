@@ -22,42 +22,55 @@
 // the latent-space V accumulation with one up-projection at the end is two_stage.py:261-277).
 #include <math.h>
 
+#include <type_traits>
+
 #include "dkv_common.cuh"
 
 namespace dkv {
 
 constexpr int D = 128;
-constexpr int NCW = 11;                // consumer warps (12 warps = 3 per SM sub-partition)
-constexpr int NTHREADS = (NCW + 1) * 32;
-constexpr int ST_TOK = 64;             // tokens per stage
+constexpr int NCW = 10;                // consumer warps; warp NCW = query rotator, warp NCW+1 = loader
+constexpr int NTHREADS = (NCW + 2) * 32;   // 12 warps = 3 per SM sub-partition
+constexpr int ST_TOK = 128;            // tokens per stage (one pair of bulk copies, one metadata block)
+constexpr int QSUB = 64;               // tokens per query-rotation sub-stage (extent of the local RoPE table)
 constexpr int GRP_PER_STAGE = ST_TOK / 16;  // 16-token groups, each handled by one consumer warp
-constexpr int NSLOT = 8;               // stages in flight (metadata slots)
-constexpr int PD = 6;                  // producer prefetch distance for lengths (stages)
-constexpr int LSTG = PD + 1;
+constexpr int NSLOT = 6;               // stages in flight
+constexpr int PD = 4;                  // loader prefetch distance for the stage metadata (stages)
+constexpr int MSLOT = NSLOT + PD;      // metadata staging slots
 constexpr int BASIS_PITCH = 272;       // bytes per basis row in smem (256 + 16: conflict-free ldmatrix)
 constexpr int Q_PITCH = 272;
 constexpr int HP = 4;                  // query heads per KV head supported by this kernel
-constexpr int RING_BYTES = 88 * 1024;
+constexpr int RING_BYTES = 72 * 1024;  // >= one worst-case stage (128 tokens x 256 B x 2 sides)
 constexpr int MAX_BATCH = 1024;
 constexpr int PART_STRIDE = 2 + 128;   // floats per (head) partial record: m, l, latent[128]
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 struct __align__(16) StageHdr {
-  uint32_t kbase;  // shared-memory byte address of the stage's K bytes
+  uint32_t kbase;   // shared-memory byte address of the stage's K bytes
   uint32_t vbase;
   int32_t n_tok;
+  int32_t start_k;  // arena element offset of the stage's first K coefficient
+  int32_t start_v;
+  int32_t elems_k;  // K elements copied for the stage (0 when the stage was rejected)
+  int32_t elems_v;
   int32_t pad;
+};
+
+struct StageMeta {   // raw slices of the cache metadata for one stage, copied asynchronously
+  int lens_k[ST_TOK];
+  int lens_v[ST_TOK];
+  int offs_k[ST_TOK];
+  int offs_v[ST_TOK];
 };
 
 struct SmemLayout {
   alignas(128) unsigned char ring[RING_BYTES];
   alignas(16) unsigned char basis[128 * BASIS_PITCH];
-  alignas(16) float4 trig[ST_TOK * 64 / 2];          // [t][nt ^ (t&7)][q] -> {c_j, s_j, c_j+1, s_j+1}
-  alignas(16) unsigned char qrot[NSLOT][HP * Q_PITCH];
-  alignas(16) unsigned long long meta[NSLOT][ST_TOK];
+  alignas(16) float4 trig[QSUB * 64 / 2];            // [t][nt ^ (t&7)][q] -> {c_j, c_j+1, s_j, s_j+1}
+  alignas(16) unsigned char qrot[NSLOT][ST_TOK / QSUB][HP * Q_PITCH];
+  alignas(16) StageMeta meta[MSLOT];
   alignas(16) StageHdr hdr[NSLOT];
   alignas(16) float merge[NCW][HP][PART_STRIDE];
-  alignas(16) int lens_stage[LSTG][132];             // kA[32] kB[32] vA[32] vB[32] goffK goffV
   alignas(16) float knorm_w[D];
   alignas(16) unsigned char zero_chunk[16];
   alignas(8) unsigned long long full_bar[NSLOT];
@@ -132,6 +145,14 @@ __device__ __forceinline__ void ldsm_x4_t_const(uint32_t (&r)[4], uint32_t addr)
       : "r"(addr));
 }
 
+// 8x8 transpose of 16-bit elements across the warp: lane (g, q) gives row g, columns 2q,2q+1 and
+// receives row g, columns 2q,2q+1 of the transposed matrix.
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t x) {
+  uint32_t y;
+  asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
 template <typename T>
 struct Mma;
 template <>
@@ -142,6 +163,12 @@ struct Mma<__nv_bfloat16> {
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ void run0(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {   // c = a.b (no accumulator input)
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
   }
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -156,6 +183,12 @@ struct Mma<__half> {
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ void run0(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
   }
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
@@ -194,7 +227,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   const int R = p.rank;
   volatile int* abort_flag = &sm.abort_flag;
 
-  // ---- prologue: partition table, barriers, basis, local-rotation table -------------------------
+  // ---- prologue A: partition table and barriers --------------------------------------------------
   if (warp == 0) {
     // inclusive scan of the per-row unit counts, 32 rows at a time
     int carry = 0;
@@ -213,36 +246,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       sm.prefix[0] = 0;
       sm.abort_flag = 0;
       for (int s = 0; s < NSLOT; ++s) {
-        mbar_init(smem_u32(&sm.full_bar[s]), 1);
-        mbar_init(smem_u32(&sm.empty_bar[s]), GRP_PER_STAGE);
+        mbar_init(smem_u32(&sm.full_bar[s]), 2);               // loader (with tx bytes) + rotator
+        mbar_init(smem_u32(&sm.empty_bar[s]), GRP_PER_STAGE);  // one arrival per 16-token group
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
   }
   if (tid < 4) reinterpret_cast<uint32_t*>(sm.zero_chunk)[tid] = 0u;
-  {
-    // basis rows [R][128] -> smem with padded pitch; rows >= R are zero
-    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.k_up) + (size_t)g * R * D);
-    for (int e = tid; e < 128 * 16; e += NTHREADS) {
-      const int r = e >> 4, c = e & 15;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < R) v = src[r * 16 + c];
-      *reinterpret_cast<uint4*>(sm.basis + r * BASIS_PITCH + c * 16) = v;
-    }
-    // local rotation table for offsets t = 0..63: angle = t * exp(-(2j/D) ln theta)
-    float* tr = reinterpret_cast<float*>(sm.trig);
-    for (int e = tid; e < ST_TOK * 64; e += NTHREADS) {
-      const int t = e >> 6, j = e & 63;
-      const float f = expf(-((float)(2 * j) / (float)D) * log_theta);
-      float sn, cs;
-      sincosf((float)t * f, &sn, &cs);
-      const int nt = j >> 3, q = (j & 7) >> 1;
-      const int idx = ((t * 8 + (nt ^ (t & 7))) * 4 + q) * 4 + (j & 1) * 2;
-      tr[idx] = cs;
-      tr[idx + 1] = sn;
-    }
-    if (KNORM && tid < D) sm.knorm_w[tid] = p.k_norm_weight[tid];
-  }
   __syncthreads();
 
   const int total_units = sm.prefix[p.batch];
@@ -273,6 +283,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   }
   if (n_stages <= 0) return;
 
+  // ---- prologue B: basis and local-rotation table (only CTAs that have work) ---------------------
+  {
+    // basis rows [R][128] -> smem with padded pitch; rows >= R are zero
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.k_up) + (size_t)g * R * D);
+    for (int e = tid; e < 128 * 16; e += NTHREADS) {
+      const int r = e >> 4, c = e & 15;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < R) v = src[r * 16 + c];
+      *reinterpret_cast<uint4*>(sm.basis + r * BASIS_PITCH + c * 16) = v;
+    }
+    // local rotation table for offsets t = 0..63: angle = t * f_j, f_j = exp(-(2j/D) ln theta).
+    // NTHREADS is a multiple of 64, so a thread keeps one j and steps t by NTHREADS/64: one exact
+    // sincos for its first t, then a fixed-angle rotation per step (error ~1e-7 per step, <= 11 steps).
+    static_assert(NTHREADS % 64 == 0, "trig table fill assumes a fixed j per thread");
+    constexpr int TSTEP = NTHREADS / 64;
+    float* tr = reinterpret_cast<float*>(sm.trig);
+    const int j = tid & 63;
+    const float f = expf(-((float)(2 * j) / (float)D) * log_theta);
+    float sn, cs, ds, dc;
+    sincosf((float)(tid >> 6) * f, &sn, &cs);
+    sincosf((float)TSTEP * f, &ds, &dc);
+    const int nt = j >> 3, q = (j & 7) >> 1;
+    for (int t = tid >> 6; t < QSUB; t += TSTEP) {
+      const int idx = ((t * 8 + (nt ^ (t & 7))) * 4 + q) * 4 + (j & 1);
+      tr[idx] = cs;
+      tr[idx + 2] = sn;
+      const float c2 = cs * dc - sn * ds, s2 = sn * dc + cs * ds;
+      cs = c2; sn = s2;
+    }
+    if (KNORM && tid < D) sm.knorm_w[tid] = p.k_norm_weight[tid];
+  }
+  __syncthreads();
+
   // first batch row touched by this CTA
   int row0 = 0;
   {
@@ -285,16 +328,70 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   }
 
   if (warp == NCW) {
-    // =========================== producer warp ===========================
+    // =========================== query rotator warp ===========================
+    // For every 64-token sub-stage with base position s0 it publishes q~ = scale * R(-s0) q for the
+    // group's heads, so that q~ . R(t) k = q . R(s0 + t) k with the local offset t = 0..63.
     const float f_lo = expf(-((float)(2 * lane) / (float)D) * log_theta);
     const float f_hi = expf(-((float)(2 * (lane + 32)) / (float)D) * log_theta);
-    float c64a, s64a, c64b, s64b;
-    sincosf((float)ST_TOK * f_lo, &s64a, &c64a);
-    sincosf((float)ST_TOK * f_hi, &s64b, &c64b);
+    float cda, sda, cdb, sdb;
+    sincosf((float)QSUB * f_lo, &sda, &cda);
+    sincosf((float)QSUB * f_hi, &sdb, &cdb);
     const float qscale = rsqrtf((float)D) * 1.4426950408889634f;  // softmax scale and log2(e) folded into q
-    float qa0[HP], qa1[HP], qb0[HP], qb1[HP];                      // rotated q: dims lane, lane+64 | lane+32, lane+96
+    float qa0[HP], qa1[HP], qb0[HP], qb1[HP];                      // dims lane, lane+64 | lane+32, lane+96
+    int row = row0;
+    for (int c = 0; c < n_stages; ++c) {
+      const int slot = c % NSLOT;
+      if (c >= NSLOT &&
+          !mbar_wait(smem_u32(&sm.empty_bar[slot]), (uint32_t)(((c / NSLOT) - 1) & 1), abort_flag))
+        break;
+      const int u = u_begin + c;
+      while (u >= sm.prefix[row + 1]) ++row;
+      const bool row_start = (c == 0) || (u == sm.prefix[row]);
+      const int b = p.batch_index ? p.batch_index[row] : row;
+      const int s0 = (u - sm.prefix[row]) * ST_TOK;
+#pragma unroll
+      for (int sub = 0; sub < ST_TOK / QSUB; ++sub) {
+        if (row_start && sub == 0) {
+          float sa, ca, sb, cb;
+          sincosf((float)s0 * f_lo, &sa, &ca);
+          sincosf((float)s0 * f_hi, &sb, &cb);
+#pragma unroll
+          for (int h = 0; h < HP; ++h) {
+            float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
+            if (h < G) {
+              const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)(g * G + h) * p.q_stride_h;
+              x0 = to_f32(qp[lane]) * qscale; x1 = to_f32(qp[lane + 64]) * qscale;
+              y0 = to_f32(qp[lane + 32]) * qscale; y1 = to_f32(qp[lane + 96]) * qscale;
+            }
+            qa0[h] = x0 * ca + x1 * sa; qa1[h] = x1 * ca - x0 * sa;
+            qb0[h] = y0 * cb + y1 * sb; qb1[h] = y1 * cb - y0 * sb;
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < HP; ++h) {
+            const float x0 = qa0[h], x1 = qa1[h], y0 = qb0[h], y1 = qb1[h];
+            qa0[h] = x0 * cda + x1 * sda; qa1[h] = x1 * cda - x0 * sda;
+            qb0[h] = y0 * cdb + y1 * sdb; qb1[h] = y1 * cdb - y0 * sdb;
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          T* qd = reinterpret_cast<T*>(sm.qrot[slot][sub] + h * Q_PITCH);
+          qd[lane] = from_f32<T>(qa0[h]); qd[lane + 64] = from_f32<T>(qa1[h]);
+          qd[lane + 32] = from_f32<T>(qb0[h]); qd[lane + 96] = from_f32<T>(qb1[h]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.full_bar[slot]));
+    }
+    return;
+  }
 
-    // length prefetch for stage c into lens_stage[c % LSTG]
+  if (warp == NCW + 1) {
+    // =========================== loader warp ===========================
+    // Per stage: copy the raw lens/offs slices into a staging slot (cp.async, PD stages ahead), read the
+    // stage's first and one-past-last arena offsets from them (rows are gap-free, so the stage is one
+    // contiguous byte range per side), take ring space, and issue the two bulk copies.
     auto prefetch = [&](int c, int row_hint) {
       if (c < n_stages) {
         const int u = u_begin + c;
@@ -304,23 +401,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         const int a = b * p.arenas_per_batch + g;
         const int s0 = (u - sm.prefix[i]) * ST_TOK;
         const int S_i = row_tokens(p, i);
-        int* dst = sm.lens_stage[c % LSTG];
+        StageMeta& dst = sm.meta[c % MSLOT];
         const int32_t* lk = p.k.lens + (size_t)a * p.k.lens_stride_a + s0;
         const int32_t* lv = p.v.lens + (size_t)a * p.v.lens_stride_a + s0;
+        const int32_t* ok = p.k.offs + (size_t)a * p.k.offs_stride_a + s0;
+        const int32_t* ov = p.v.offs + (size_t)a * p.v.offs_stride_a + s0;
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
+        for (int hh = 0; hh < ST_TOK / 32; ++hh) {
           const int t = lane + 32 * hh;
           if (s0 + t < S_i) {
-            cp_async4(smem_u32(dst + t), lk + t);
-            cp_async4(smem_u32(dst + 64 + t), lv + t);
+            cp_async4(smem_u32(&dst.lens_k[t]), lk + t);
+            cp_async4(smem_u32(&dst.lens_v[t]), lv + t);
+            cp_async4(smem_u32(&dst.offs_k[t]), ok + t);
+            cp_async4(smem_u32(&dst.offs_v[t]), ov + t);
           } else {
-            dst[t] = 0;
-            dst[64 + t] = 0;
+            dst.lens_k[t] = 0; dst.lens_v[t] = 0; dst.offs_k[t] = 0; dst.offs_v[t] = 0;
           }
-        }
-        if (lane == 0) {
-          cp_async4(smem_u32(dst + 128), p.k.offs + (size_t)a * p.k.offs_stride_a + s0);
-          cp_async4(smem_u32(dst + 129), p.v.offs + (size_t)a * p.v.offs_stride_a + s0);
         }
       }
       cp_async_commit();
@@ -328,74 +424,53 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     for (int c = 0; c < PD; ++c) prefetch(c, row0);
 
     int row = row0;
-    int head = 0;         // ring allocation cursor (lane 0 owns the allocator; kept warp-uniform)
+    int head = 0;         // ring allocation cursor (state is kept identical on all lanes)
     int oldest = 0;       // oldest stage whose ring bytes are still owned by consumers
     bool wrapped = false;
     bool ok = true;
+    auto release_oldest = [&](int c) -> bool {
+      const bool done = mbar_wait(smem_u32(&sm.empty_bar[oldest % NSLOT]), (uint32_t)((oldest / NSLOT) & 1), abort_flag);
+      if (!done) return false;
+      const int old_start = sm.ring_start[oldest % NSLOT];
+      ++oldest;
+      if (oldest < c) {
+        const int new_start = sm.ring_start[oldest % NSLOT];
+        if (new_start < old_start) wrapped = false;
+      } else {
+        head = 0;
+        wrapped = false;
+      }
+      return true;
+    };
     for (int c = 0; c < n_stages && ok; ++c) {
+      const int slot = c % NSLOT;
+      // the stage that last used this slot (and the staging slot the next prefetch overwrites) must be done
+      while (ok && oldest <= c - NSLOT) ok = release_oldest(c);
+      if (!ok) break;
       prefetch(c + PD, row);
       cp_async_wait<PD>();
       __syncwarp();
       const int u = u_begin + c;
       while (u >= sm.prefix[row + 1]) ++row;
-      const bool row_start = (c == 0) || (u == sm.prefix[row]);
       const int b = p.batch_index ? p.batch_index[row] : row;
       const int a = b * p.arenas_per_batch + g;
       const int s0 = (u - sm.prefix[row]) * ST_TOK;
       const int n_tok = min(ST_TOK, row_tokens(p, row) - s0);
-      const int* ls = sm.lens_stage[c % LSTG];
-      int kA = ls[lane], kB = ls[32 + lane], vA = ls[64 + lane], vB = ls[96 + lane];
-      const int goffK = ls[128], goffV = ls[129];
-      {
-        const int bad = (kA | kB | vA | vB);
-        const bool is_bad = (bad & 7) != 0 || bad < 0 || kA > R || kB > R || vA > R || vB > R;
-        if (__any_sync(0xffffffffu, is_bad)) {
-          if (lane == 0) set_status(p.status, DKV_ST_BAD_LENGTH);
-          kA = min(max(kA, 0), R) & ~7; kB = min(max(kB, 0), R) & ~7;
-          vA = min(max(vA, 0), R) & ~7; vB = min(max(vB, 0), R) & ~7;
-        }
-        if (((goffK | goffV) & 7) != 0 || goffK < 0 || goffV < 0) {
-          // a misaligned arena offset cannot be bulk-copied: drop the stage's payload, keep going
-          if (lane == 0) set_status(p.status, DKV_ST_BAD_LENGTH);
-          kA = kB = vA = vB = 0;
-        }
-      }
-      // exclusive scans (tokens 0..31 on the A registers, 32..63 on the B registers)
-      int ik = kA, iv = vA, jk = kB, jv = vB;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int t0 = __shfl_up_sync(0xffffffffu, ik, o), t1 = __shfl_up_sync(0xffffffffu, iv, o);
-        const int t2 = __shfl_up_sync(0xffffffffu, jk, o), t3 = __shfl_up_sync(0xffffffffu, jv, o);
-        if (lane >= o) { ik += t0; iv += t1; jk += t2; jv += t3; }
-      }
-      const int totKA = __shfl_sync(0xffffffffu, ik, 31), totVA = __shfl_sync(0xffffffffu, iv, 31);
-      const int totK = totKA + __shfl_sync(0xffffffffu, jk, 31), totV = totVA + __shfl_sync(0xffffffffu, jv, 31);
-      const int offKA = ik - kA, offKB = totKA + jk - kB, offVA = iv - vA, offVB = totVA + jv - vB;  // elements
-      if ((int64_t)goffK + totK > p.k.flat_stride || (int64_t)goffV + totV > p.v.flat_stride) {
-        if (lane == 0) set_status(p.status, DKV_ST_OVERFLOW);   // metadata points past the arena row
-        *abort_flag = 1;
-        ok = false;
-        break;
+      const StageMeta& mt = sm.meta[c % MSLOT];
+      const int startK = mt.offs_k[0], startV = mt.offs_v[0];
+      const int endK = mt.offs_k[n_tok - 1] + mt.lens_k[n_tok - 1];
+      const int endV = mt.offs_v[n_tok - 1] + mt.lens_v[n_tok - 1];
+      int totK = endK - startK, totV = endV - startV;
+      // the byte ranges must be 16-byte aligned, inside the arena row and no larger than a full stage
+      const bool bad = ((startK | startV | endK | endV) & 7) != 0 || startK < 0 || startV < 0 || totK < 0 ||
+                       totV < 0 || totK > ST_TOK * 128 || totV > ST_TOK * 128 ||
+                       (int64_t)endK > p.k.flat_stride || (int64_t)endV > p.v.flat_stride;
+      if (bad) {
+        if (lane == 0) set_status(p.status, DKV_ST_BAD_LENGTH);
+        totK = 0; totV = 0;     // consumers see an empty stage and skip its tokens
       }
       const int bytesK = totK * 2, bytesV = totV * 2, need = bytesK + bytesV;
 
-      // ---- slot + ring space (allocator state is identical on all lanes) ----
-      const int slot = c % NSLOT;
-      auto release_oldest = [&]() -> bool {
-        const bool done = mbar_wait(smem_u32(&sm.empty_bar[oldest % NSLOT]), (uint32_t)((oldest / NSLOT) & 1), abort_flag);
-        if (!done) return false;
-        const int old_start = sm.ring_start[oldest % NSLOT];
-        ++oldest;
-        if (oldest < c) {
-          const int new_start = sm.ring_start[oldest % NSLOT];
-          if (new_start < old_start) wrapped = false;
-        } else {
-          head = 0;
-          wrapped = false;
-        }
-        return true;
-      };
-      while (ok && oldest <= c - NSLOT) ok = release_oldest();
       int start = 0;
       while (ok) {
         if (oldest == c) { start = 0; head = 0; wrapped = false; break; }
@@ -406,69 +481,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         } else {
           if (head + need <= tail) { start = head; break; }
         }
-        ok = release_oldest();
+        ok = release_oldest(c);
       }
       if (!ok) break;
       head = start + need;
       __syncwarp();
-      if (lane == 0) sm.ring_start[slot] = start;
-
-      // ---- stage metadata ----
-      {
-        const unsigned long long mA = (unsigned long long)(offKA >> 3) | ((unsigned long long)(offVA >> 3) << 16) |
-                                      ((unsigned long long)kA << 32) | ((unsigned long long)vA << 40);
-        const unsigned long long mB = (unsigned long long)(offKB >> 3) | ((unsigned long long)(offVB >> 3) << 16) |
-                                      ((unsigned long long)kB << 32) | ((unsigned long long)vB << 40);
-        sm.meta[slot][lane] = mA;
-        sm.meta[slot][32 + lane] = mB;
-        if (lane == 0) {
-          StageHdr h;
-          h.kbase = smem_u32(sm.ring + start);
-          h.vbase = smem_u32(sm.ring + start + bytesK);
-          h.n_tok = n_tok;
-          h.pad = 0;
-          sm.hdr[slot] = h;
-        }
+      const uint32_t bar = smem_u32(&sm.full_bar[slot]);
+      const uint32_t kbase = smem_u32(sm.ring + start), vbase = kbase + (uint32_t)bytesK;
+      if (lane == 0) {
+        sm.ring_start[slot] = start;
+        StageHdr h;
+        h.kbase = kbase;
+        h.vbase = vbase;
+        h.n_tok = n_tok;
+        h.start_k = startK; h.start_v = startV;
+        h.elems_k = totK; h.elems_v = totV;
+        h.pad = 0;
+        sm.hdr[slot] = h;
+        mbar_arrive_expect_tx(bar, (uint32_t)need);
       }
-      // ---- queries rotated back by the stage base position ----
-      if (row_start) {
-        float sa, ca, sb, cb;
-        sincosf((float)s0 * f_lo, &sa, &ca);
-        sincosf((float)s0 * f_hi, &sb, &cb);
-#pragma unroll
-        for (int h = 0; h < HP; ++h) {
-          float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
-          if (h < G) {
-            const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)(g * G + h) * p.q_stride_h;
-            x0 = to_f32(qp[lane]) * qscale; x1 = to_f32(qp[lane + 64]) * qscale;
-            y0 = to_f32(qp[lane + 32]) * qscale; y1 = to_f32(qp[lane + 96]) * qscale;
-          }
-          qa0[h] = x0 * ca + x1 * sa; qa1[h] = x1 * ca - x0 * sa;
-          qb0[h] = y0 * cb + y1 * sb; qb1[h] = y1 * cb - y0 * sb;
-        }
-      } else {
-#pragma unroll
-        for (int h = 0; h < HP; ++h) {
-          const float x0 = qa0[h], x1 = qa1[h], y0 = qb0[h], y1 = qb1[h];
-          qa0[h] = x0 * c64a + x1 * s64a; qa1[h] = x1 * c64a - x0 * s64a;
-          qb0[h] = y0 * c64b + y1 * s64b; qb1[h] = y1 * c64b - y0 * s64b;
-        }
-      }
-#pragma unroll
-      for (int h = 0; h < HP; ++h) {
-        T* qd = reinterpret_cast<T*>(sm.qrot[slot] + h * Q_PITCH);
-        qd[lane] = from_f32<T>(qa0[h]); qd[lane + 64] = from_f32<T>(qa1[h]);
-        qd[lane + 32] = from_f32<T>(qb0[h]); qd[lane + 96] = from_f32<T>(qb1[h]);
+      // A thread sustains only a few bulk copies per microsecond, so the stage's two byte ranges are cut in
+      // halves and issued by four lanes (side = lane & 1, half = lane >> 1); all complete on the same barrier.
+      if (lane < 4) {
+        const int side = lane & 1, half = lane >> 1;
+        const int bytes = side ? bytesV : bytesK;
+        const int first = (bytes / 2) & ~15;                 // 16-byte aligned split point
+        const int off = half ? first : 0, len = half ? bytes - first : first;
+        const T* src = side ? reinterpret_cast<const T*>(p.v.flat) + (size_t)a * p.v.flat_stride + startV
+                            : reinterpret_cast<const T*>(p.k.flat) + (size_t)a * p.k.flat_stride + startK;
+        if (len > 0)
+          bulk_g2s((side ? vbase : kbase) + (uint32_t)off, reinterpret_cast<const unsigned char*>(src) + off,
+                   (uint32_t)len, bar);
       }
       __syncwarp();
-      if (lane == 0) {
-        const uint32_t bar = smem_u32(&sm.full_bar[slot]);
-        mbar_arrive_expect_tx(bar, (uint32_t)need);
-        const T* kf = reinterpret_cast<const T*>(p.k.flat) + (size_t)a * p.k.flat_stride + goffK;
-        const T* vf = reinterpret_cast<const T*>(p.v.flat) + (size_t)a * p.v.flat_stride + goffV;
-        if (bytesK > 0) bulk_g2s(smem_u32(sm.ring + start), kf, (uint32_t)bytesK, bar);
-        if (bytesV > 0) bulk_g2s(smem_u32(sm.ring + start + bytesK), vf, (uint32_t)bytesV, bar);
-      }
     }
     cp_async_wait<0>();
     if (!ok && lane == 0) set_status(p.status, DKV_ST_OVERFLOW);
@@ -487,7 +532,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   int grp = warp;             // next group of this warp
   while (row < p.batch && sm.prefix[row] < u_end) {
     const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;   // stages of this row: [.., c_hi)
-    float m_run = -INFINITY, l_part = 0.f;
+    float m_run0 = -INFINITY, m_run1 = -INFINITY, l_part0 = 0.f, l_part1 = 0.f;   // heads 2qq, 2qq+1
     float oacc[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
@@ -498,31 +543,43 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       if (*abort_flag) continue;
       if (!mbar_wait(smem_u32(&sm.full_bar[slot]), (uint32_t)((c / NSLOT) & 1), abort_flag)) continue;
       const StageHdr hdr = sm.hdr[slot];
-      const int tl = lane & 15;
-      unsigned long long meta = 0ull;
-      if (gi * 16 < hdr.n_tok) meta = sm.meta[slot][gi * 16 + tl];
-      const int klen = (int)((meta >> 32) & 0xff), vlen = (int)((meta >> 40) & 0xff);
-      const uint32_t koff = (uint32_t)(meta & 0xffff), voff = (uint32_t)((meta >> 16) & 0xffff);
+      const StageMeta& mt = sm.meta[c % MSLOT];
+      const int tok = gi * 16 + (lane & 15);     // lanes 16..31 mirror lanes 0..15
+      int klen = 0, vlen = 0;
+      uint32_t koff = 0u, voff = 0u;             // 16-byte chunks from the stage's K / V base
+      if (tok < hdr.n_tok) {
+        klen = mt.lens_k[tok];
+        vlen = mt.lens_v[tok];
+        const int ko = mt.offs_k[tok] - hdr.start_k, vo = mt.offs_v[tok] - hdr.start_v;   // elements
+        const bool bad_k = ((klen | ko) & 7) != 0 || klen < 0 || klen > R || ko < 0 || ko + klen > hdr.elems_k;
+        const bool bad_v = ((vlen | vo) & 7) != 0 || vlen < 0 || vlen > R || vo < 0 || vo + vlen > hdr.elems_v;
+        if (bad_k || bad_v) {   // breaks the layout contract: the token is dropped and the call flagged
+          set_status(p.status, DKV_ST_BAD_LENGTH);
+          if (bad_k) klen = 0;
+          vlen = 0;
+        }
+        koff = (uint32_t)ko >> 3;
+        voff = (uint32_t)vo >> 3;
+      }
       const uint32_t valid = __ballot_sync(0xffffffffu, klen > 0) & 0xffffu;
       if (valid != 0u) {
         const int kmax = __reduce_max_sync(0xffffffffu, klen);
         const int vmax = __reduce_max_sync(0xffffffffu, vlen);
         // ---------------- K = X . Bk ----------------
         float acc[16][4];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
         const uint32_t krow = hdr.kbase + koff * 16u;
         const int cpar16 = lane >> 4;
         uint32_t a[4];
         ldsm_x4(a, (cpar16 * 8 < klen) ? krow + cpar16 * 16 : zero_addr);
-        for (int ks = 0; ks * 16 < kmax; ++ks) {
-          // next k-step's coefficient fragment while the tensor pipe works on this one
+        // one k-step = 16 latent coefficients: basis fragments are fetched four ldmatrix at a time ahead of
+        // the eight MMAs that use them, and the next step's coefficient fragment is loaded meanwhile.
+        // The first step writes the accumulators (no zero fill), later steps add to them.
+        auto kstep = [&](int ks, auto first) {
           uint32_t an[4] = {0u, 0u, 0u, 0u};
           if ((ks + 1) * 16 < kmax) {
             const int chunk = 2 * (ks + 1) + cpar16;
             ldsm_x4(an, (chunk * 8 < klen) ? krow + chunk * 16 : zero_addr);
           }
-          // basis fragments are fetched four ldmatrix at a time, ahead of the eight MMAs that use them
           const uint32_t brow = basis_lane + ks * 16 * BASIS_PITCH;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
@@ -532,12 +589,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int ntp = half * 4 + j;
-              Mma<T>::run(acc[2 * ntp], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
-              Mma<T>::run(acc[2 * ntp + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
+              if (decltype(first)::value) {
+                Mma<T>::run0(acc[2 * ntp], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
+                Mma<T>::run0(acc[2 * ntp + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
+              } else {
+                Mma<T>::run(acc[2 * ntp], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
+                Mma<T>::run(acc[2 * ntp + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
+              }
             }
           }
           a[0] = an[0]; a[1] = an[1]; a[2] = an[2]; a[3] = an[3];
-        }
+        };
+        kstep(0, std::true_type{});
+        for (int ks = 1; ks * 16 < kmax; ++ks) kstep(ks, std::false_type{});
         // ---------------- optional RMSNorm of K (Qwen3) ----------------
         float rs0 = 1.f, rs1 = 1.f;
         if (KNORM) {
@@ -558,62 +622,74 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
             acc[i][2] *= w.x * rs1; acc[i][3] *= w.y * rs1;
           }
         }
-        // ---------------- local RoPE, pack to 16-bit B fragments ----------------
+        // ---------------- local RoPE (packed fp32 pairs), pack to 16-bit A fragments ----------------
         uint32_t kb[16][2];
         {
-          const int tA = gi * 16 + gq, tB = tA + 8;
+          const int tA = (gi & (QSUB / 16 - 1)) * 16 + gq, tB = tA + 8;   // offset inside the 64-token sub-stage
 #pragma unroll
           for (int nt = 0; nt < 8; ++nt) {
-            const float4 ta = trig4[(tA * 8 + (nt ^ (tA & 7))) * 4 + qq];
+            const float4 ta = trig4[(tA * 8 + (nt ^ (tA & 7))) * 4 + qq];   // {c_j, c_j+1, s_j, s_j+1}
             const float4 tb = trig4[(tB * 8 + (nt ^ (tB & 7))) * 4 + qq];
-            const float lo0 = acc[nt][0], lo1 = acc[nt][1], hi0 = acc[nt + 8][0], hi1 = acc[nt + 8][1];
-            kb[nt][0] = Mma<T>::pack(lo0 * ta.x - hi0 * ta.y, lo1 * ta.z - hi1 * ta.w);
-            kb[nt + 8][0] = Mma<T>::pack(hi0 * ta.x + lo0 * ta.y, hi1 * ta.z + lo1 * ta.w);
-            const float lo2 = acc[nt][2], lo3 = acc[nt][3], hi2 = acc[nt + 8][2], hi3 = acc[nt + 8][3];
-            kb[nt][1] = Mma<T>::pack(lo2 * tb.x - hi2 * tb.y, lo3 * tb.z - hi3 * tb.w);
-            kb[nt + 8][1] = Mma<T>::pack(hi2 * tb.x + lo2 * tb.y, hi3 * tb.z + lo3 * tb.w);
+            {
+              const float2 lo = make_float2(acc[nt][0], acc[nt][1]), hi = make_float2(acc[nt + 8][0], acc[nt + 8][1]);
+              const float2 C = make_float2(ta.x, ta.y), S = make_float2(ta.z, ta.w);
+              const float2 u = __fmul2_rn(hi, S);
+              const float2 lo2 = __ffma2_rn(lo, C, make_float2(-u.x, -u.y));
+              const float2 hi2 = __ffma2_rn(lo, S, __fmul2_rn(hi, C));
+              kb[nt][0] = Mma<T>::pack(lo2.x, lo2.y);
+              kb[nt + 8][0] = Mma<T>::pack(hi2.x, hi2.y);
+            }
+            {
+              const float2 lo = make_float2(acc[nt][2], acc[nt][3]), hi = make_float2(acc[nt + 8][2], acc[nt + 8][3]);
+              const float2 C = make_float2(tb.x, tb.y), S = make_float2(tb.z, tb.w);
+              const float2 u = __fmul2_rn(hi, S);
+              const float2 lo2 = __ffma2_rn(lo, C, make_float2(-u.x, -u.y));
+              const float2 hi2 = __ffma2_rn(lo, S, __fmul2_rn(hi, C));
+              kb[nt][1] = Mma<T>::pack(lo2.x, lo2.y);
+              kb[nt + 8][1] = Mma<T>::pack(hi2.x, hi2.y);
+            }
           }
         }
-        // ---------------- S^T[heads x tokens] = Q~ . K'^T ----------------
-        float s_lo[4] = {0.f, 0.f, 0.f, 0.f}, s_hi[4] = {0.f, 0.f, 0.f, 0.f};  // tokens 0-7 / 8-15
+        // ---------------- S[tokens x heads] = K' . Q~^T ----------------
+        // accumulator fragments of K' double as the A operand; the rotated queries are the B operand
+        float sacc[4];
         {
-          // ldmatrix rows 0..3 = heads, rows 4..7 read the zero chunk
-          const uint32_t qbase = smem_u32(sm.qrot[slot]);
+          // ldmatrix rows 0..HP-1 = heads, the other rows read the zero chunk
+          const uint32_t qbase = smem_u32(sm.qrot[slot][gi / (QSUB / 16)]);
           const int qr = lane & 7;
           const uint32_t qaddr = (qr < HP) ? qbase + qr * Q_PITCH + (lane >> 3) * 16 : zero_addr;
           uint32_t qa[4][4];
 #pragma unroll
-          for (int kp = 0; kp < 4; ++kp)   // {kd=2kp: d 0-7, d 8-15 ; kd=2kp+1: d 0-7, d 8-15}
+          for (int kp = 0; kp < 4; ++kp)   // {d-step 2kp: dims 0-7, 8-15 ; d-step 2kp+1: dims 0-7, 8-15}
             ldsm_x4(qa[kp], (qr < HP) ? qaddr + kp * 64 : zero_addr);
+          Mma<T>::run0(sacc, kb[0][0], kb[0][1], kb[1][0], kb[1][1], qa[0][0], qa[0][1]);
+          Mma<T>::run(sacc, kb[2][0], kb[2][1], kb[3][0], kb[3][1], qa[0][2], qa[0][3]);
 #pragma unroll
-          for (int kp = 0; kp < 4; ++kp) {
-            Mma<T>::run(s_lo, qa[kp][0], 0u, qa[kp][1], 0u, kb[4 * kp][0], kb[4 * kp + 1][0]);
-            Mma<T>::run(s_hi, qa[kp][0], 0u, qa[kp][1], 0u, kb[4 * kp][1], kb[4 * kp + 1][1]);
-            Mma<T>::run(s_lo, qa[kp][2], 0u, qa[kp][3], 0u, kb[4 * kp + 2][0], kb[4 * kp + 3][0]);
-            Mma<T>::run(s_hi, qa[kp][2], 0u, qa[kp][3], 0u, kb[4 * kp + 2][1], kb[4 * kp + 3][1]);
+          for (int kp = 1; kp < 4; ++kp) {
+            Mma<T>::run(sacc, kb[4 * kp][0], kb[4 * kp][1], kb[4 * kp + 1][0], kb[4 * kp + 1][1], qa[kp][0], qa[kp][1]);
+            Mma<T>::run(sacc, kb[4 * kp + 2][0], kb[4 * kp + 2][1], kb[4 * kp + 3][0], kb[4 * kp + 3][1], qa[kp][2], qa[kp][3]);
           }
         }
         // ---------------- online softmax (base 2) ----------------
-        float sc0 = s_lo[0], sc1 = s_lo[1], sc2 = s_hi[0], sc3 = s_hi[1];   // tokens 2q, 2q+1, 8+2q, 9+2q
-        if (KNORM) {
-          // scores scale with 1/rms of their token: fetch it from the lane that owns the token row
-          // (already folded into acc above, nothing to do)
+        // this lane: tokens gq and gq+8, heads 2qq and 2qq+1; head maxima are reduced over the 8 token lanes
+        float sc0 = sacc[0], sc1 = sacc[1], sc2 = sacc[2], sc3 = sacc[3];
+        if (!((valid >> gq) & 1u)) { sc0 = -INFINITY; sc1 = -INFINITY; }
+        if (!((valid >> (gq + 8)) & 1u)) { sc2 = -INFINITY; sc3 = -INFINITY; }
+        float mx0 = fmaxf(sc0, sc2), mx1 = fmaxf(sc1, sc3);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
         }
-        if (!((valid >> (2 * qq)) & 1u)) sc0 = -INFINITY;
-        if (!((valid >> (2 * qq + 1)) & 1u)) sc1 = -INFINITY;
-        if (!((valid >> (8 + 2 * qq)) & 1u)) sc2 = -INFINITY;
-        if (!((valid >> (9 + 2 * qq)) & 1u)) sc3 = -INFINITY;
-        float mx = fmaxf(fmaxf(sc0, sc1), fmaxf(sc2, sc3));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float alpha = exp2f(m_run - m_new);
-        const float p0 = exp2f(sc0 - m_new), p1 = exp2f(sc1 - m_new), p2 = exp2f(sc2 - m_new), p3 = exp2f(sc3 - m_new);
-        l_part = l_part * alpha + (p0 + p1) + (p2 + p3);
-        m_run = m_new;
-        const uint32_t pb0 = Mma<T>::pack(p0, p1), pb1 = Mma<T>::pack(p2, p3);
-        const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * qq), al1 = __shfl_sync(0xffffffffu, alpha, 8 * qq + 4);
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+        const float mn0 = fmaxf(m_run0, mx0), mn1 = fmaxf(m_run1, mx1);
+        const float al0 = exp2f(m_run0 - mn0), al1 = exp2f(m_run1 - mn1);
+        const float p0 = exp2f(sc0 - mn0), p1 = exp2f(sc1 - mn1), p2 = exp2f(sc2 - mn0), p3 = exp2f(sc3 - mn1);
+        l_part0 = l_part0 * al0 + (p0 + p2);
+        l_part1 = l_part1 * al1 + (p1 + p3);
+        m_run0 = mn0; m_run1 = mn1;
+        // P[tokens x heads] -> B operand [token pairs x head] by an 8x8 transpose per token half
+        const uint32_t pb0 = movmatrix_t(Mma<T>::pack(p0, p1)), pb1 = movmatrix_t(Mma<T>::pack(p2, p3));
+        if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) { oacc[i][0] *= al0; oacc[i][1] *= al1; oacc[i][2] *= al0; oacc[i][3] *= al1; }
         }
@@ -643,9 +719,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
 
     // ---------------- row flush: merge the consumer warps' partial states ----------------
-    l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
-    l_part += __shfl_xor_sync(0xffffffffu, l_part, 2);
-    if (gq < HP && qq == 0) { sm.merge[warp][gq][0] = m_run; sm.merge[warp][gq][1] = l_part; }
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      l_part0 += __shfl_xor_sync(0xffffffffu, l_part0, o);
+      l_part1 += __shfl_xor_sync(0xffffffffu, l_part1, o);
+    }
+    if (gq == 0) {
+      if (2 * qq < HP) { sm.merge[warp][2 * qq][0] = m_run0; sm.merge[warp][2 * qq][1] = l_part0; }
+      if (2 * qq + 1 < HP) { sm.merge[warp][2 * qq + 1][0] = m_run1; sm.merge[warp][2 * qq + 1][1] = l_part1; }
+    }
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) {
       const int r = 16 * mt + gq;
@@ -722,50 +804,99 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 }
 
 // Merge the split partials of one (batch row, query head) and project through Bv.
+// 128 threads; the partial records of the row are read with independent loads (weights first, then the
+// latent vectors 8 records at a time) so the kernel is not a chain of dependent L2 round trips.
+constexpr int COMBINE_MAX_PART = 160;   // >= CTAs per KV head (at most the SM count)
 template <typename T>
 __global__ void __launch_bounds__(128) split_combine_kernel(dkv_attn_args p) {
   __shared__ float lat_s[128];
+  __shared__ float wgt_s[COMBINE_MAX_PART];
+  __shared__ float red_s[4][128];
   const WsHeader* wh = reinterpret_cast<const WsHeader*>(p.workspace);
   const float* ws = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(p.workspace) + ws_header_bytes());
-  const int i = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int i = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = p.n_q_heads / p.n_basis_groups, g = h / G, hl = h - g * G, R = p.rank;
   const int n_cta = wh->n_cta, total_units = wh->total_units;
   const int u_lo = wh->prefix[i], u_hi = wh->prefix[i + 1];
   const size_t entries_per_group = (size_t)p.batch + n_cta;
   // CTA k of this KV head covered units [unit_begin(k), unit_begin(k+1)); those that overlap this row's
   // units [u_lo, u_hi) each left one partial record at entry (row + k).
-  auto overlaps = [&](int k) {
-    const int ub = unit_begin(k, n_cta, total_units), ue = unit_begin(k + 1, n_cta, total_units);
-    return ue > ub && ub < u_hi && ue > u_lo;
-  };
   int k_lo = 0, k_hi = -1;
   if (u_hi > u_lo && total_units > 0) {
-    // first CTA whose range ends after u_lo, last CTA whose range starts before u_hi
     k_lo = (int)(((long long)u_lo * n_cta) / total_units);
     while (k_lo > 0 && unit_begin(k_lo, n_cta, total_units) > u_lo) --k_lo;
     k_hi = min(n_cta - 1, (int)(((long long)u_hi * n_cta + total_units - 1) / total_units));
   }
+  const float* rec0 = ws + (((size_t)g * entries_per_group + (size_t)i) * HP + hl) * PART_STRIDE;
+  const size_t rec_step = (size_t)HP * PART_STRIDE;   // record k sits at rec0 + k * rec_step
+  // pass 1: thread t looks at candidate CTA k_lo + t (the range never exceeds the block in practice; loop anyway)
+  float m_mine = -INFINITY, l_mine = 0.f;
   float M = -INFINITY;
-  for (int k = k_lo; k <= k_hi; ++k) {
-    if (!overlaps(k)) continue;
-    const float* rec = ws + (((size_t)g * entries_per_group + (size_t)i + k) * HP + hl) * PART_STRIDE;
-    M = fmaxf(M, rec[0]);
+  for (int base = k_lo; base <= k_hi; base += 128) {
+    const int k = base + tid;
+    float mk = -INFINITY;
+    if (k <= k_hi) {
+      const int ub = unit_begin(k, n_cta, total_units), ue = unit_begin(k + 1, n_cta, total_units);
+      if (ue > ub && ub < u_hi && ue > u_lo) { mk = rec0[k * rec_step]; l_mine = rec0[k * rec_step + 1]; m_mine = mk; }
+    }
+    M = fmaxf(M, mk);
   }
-  float v = 0.f, L = 0.f;
-  for (int k = k_lo; k <= k_hi; ++k) {
-    if (!overlaps(k)) continue;
-    const float* rec = ws + (((size_t)g * entries_per_group + (size_t)i + k) * HP + hl) * PART_STRIDE;
-    const float mw = rec[0];
-    const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-    v = fmaf(rec[2 + tid], wgt, v);
-    L = fmaf(rec[1], wgt, L);
+  M = warp_max(M);
+  if (lane == 0) red_s[0][warp] = M;
+  __syncthreads();
+  M = fmaxf(fmaxf(red_s[0][0], red_s[0][1]), fmaxf(red_s[0][2], red_s[0][3]));
+  __syncthreads();
+  // weights (k_hi - k_lo < 128 whenever the grid has at most 128 CTAs per head per row; larger ranges fall
+  // back to recomputing weights below)
+  const int span = k_hi - k_lo + 1;
+  const bool fits = span <= 128 && span <= COMBINE_MAX_PART;
+  float w_mine = (m_mine == -INFINITY) ? 0.f : exp2f(m_mine - M);
+  if (fits && tid < span) wgt_s[tid] = w_mine;
+  float L = warp_sum(w_mine * l_mine);
+  if (lane == 0) red_s[1][warp] = L;
+  __syncthreads();
+  L = red_s[1][0] + red_s[1][1] + red_s[1][2] + red_s[1][3];
+  // pass 2: latent vector, thread = latent index
+  float v = 0.f;
+  if (fits) {
+    int kk = 0;
+    for (; kk + 8 <= span; kk += 8) {
+      float x[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = wgt_s[kk + j] != 0.f ? rec0[(size_t)(k_lo + kk + j) * rec_step + 2 + tid] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v = fmaf(x[j], wgt_s[kk + j], v);
+    }
+    for (; kk < span; ++kk)
+      if (wgt_s[kk] != 0.f) v = fmaf(rec0[(size_t)(k_lo + kk) * rec_step + 2 + tid], wgt_s[kk], v);
+  } else {
+    L = 0.f;
+    for (int k = k_lo; k <= k_hi; ++k) {
+      const int ub = unit_begin(k, n_cta, total_units), ue = unit_begin(k + 1, n_cta, total_units);
+      if (!(ue > ub && ub < u_hi && ue > u_lo)) continue;
+      const float mw = rec0[k * rec_step];
+      const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      v = fmaf(rec0[k * rec_step + 2 + tid], wgt, v);
+      L = fmaf(rec0[k * rec_step + 1], wgt, L);
+    }
   }
   lat_s[tid] = L > 0.f ? v / L : 0.f;
   if (L <= 0.f && tid == 0) set_status(p.status, DKV_ST_EMPTY_ROW);
   __syncthreads();
+  // projection: warp w takes latent rows w, w+4, ...; lane covers 4 output dims; partial sums merged in smem
   const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * D;
-  float o = 0.f;
-  for (int r = 0; r < R; ++r) o = fmaf(lat_s[r], to_f32(vup[(size_t)r * D + tid]), o);
+  float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll 4
+  for (int r = warp; r < R; r += 4) {
+    const float lr = lat_s[r];
+    const T* row = vup + (size_t)r * D + lane * 4;
+    o0 = fmaf(lr, to_f32(row[0]), o0); o1 = fmaf(lr, to_f32(row[1]), o1);
+    o2 = fmaf(lr, to_f32(row[2]), o2); o3 = fmaf(lr, to_f32(row[3]), o3);
+  }
+  red_s[warp][lane * 4 + 0] = o0; red_s[warp][lane * 4 + 1] = o1;
+  red_s[warp][lane * 4 + 2] = o2; red_s[warp][lane * 4 + 3] = o3;
+  __syncthreads();
+  const float o = red_s[0][tid] + red_s[1][tid] + red_s[2][tid] + red_s[3][tid];
   const int b = p.batch_index ? p.batch_index[i] : i;
   T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)h * p.out_stride_h;
   op[tid] = from_f32<T>(o);

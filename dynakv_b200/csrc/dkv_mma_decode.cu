@@ -29,8 +29,8 @@
 namespace dkv {
 
 constexpr int D = 128;
-constexpr int NCW = 10;                // consumer warps; warp NCW = query rotator, warp NCW+1 = loader
-constexpr int NTHREADS = (NCW + 2) * 32;   // 12 warps = 3 per SM sub-partition
+constexpr int NCW = 9;                 // consumer warps; warp NCW = query rotator, NCW+1 / NCW+2 = K / V loader
+constexpr int NTHREADS = (NCW + 3) * 32;   // 12 warps = 3 per SM sub-partition
 constexpr int ST_TOK = 128;            // tokens per stage (one pair of bulk copies, one metadata block)
 constexpr int QSUB = 64;               // tokens per query-rotation sub-stage (extent of the local RoPE table)
 constexpr int GRP_PER_STAGE = ST_TOK / 16;  // 16-token groups, each handled by one consumer warp
@@ -40,43 +40,37 @@ constexpr int MSLOT = NSLOT + PD;      // metadata staging slots
 constexpr int BASIS_PITCH = 272;       // bytes per basis row in smem (256 + 16: conflict-free ldmatrix)
 constexpr int Q_PITCH = 272;
 constexpr int HP = 4;                  // query heads per KV head supported by this kernel
-constexpr int RING_BYTES = 72 * 1024;  // >= one worst-case stage (128 tokens x 256 B x 2 sides)
+constexpr int RING_BYTES = 36 * 1024;  // per side; >= one worst-case stage (128 tokens x 256 B)
 constexpr int MAX_BATCH = 1024;
 constexpr int PART_STRIDE = 2 + 128;   // floats per (head) partial record: m, l, latent[128]
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
-struct __align__(16) StageHdr {
-  uint32_t kbase;   // shared-memory byte address of the stage's K bytes
-  uint32_t vbase;
+struct __align__(16) StageHdr {   // one side (K or V) of one stage
+  uint32_t base;    // shared-memory byte address of the stage's bytes
   int32_t n_tok;
-  int32_t start_k;  // arena element offset of the stage's first K coefficient
-  int32_t start_v;
-  int32_t elems_k;  // K elements copied for the stage (0 when the stage was rejected)
-  int32_t elems_v;
-  int32_t pad;
+  int32_t start;    // arena element offset of the stage's first coefficient
+  int32_t elems;    // elements copied for the stage (0 when the stage was rejected)
 };
 
-struct StageMeta {   // raw slices of the cache metadata for one stage, copied asynchronously
-  int lens_k[ST_TOK];
-  int lens_v[ST_TOK];
-  int offs_k[ST_TOK];
-  int offs_v[ST_TOK];
+struct StageMeta {   // raw slices of one side's cache metadata for one stage, copied asynchronously
+  alignas(16) int lens[ST_TOK];
+  alignas(16) int offs[ST_TOK];
 };
 
 struct SmemLayout {
-  alignas(128) unsigned char ring[RING_BYTES];
+  alignas(128) unsigned char ring[2][RING_BYTES];
   alignas(16) unsigned char basis[128 * BASIS_PITCH];
   alignas(16) float4 trig[QSUB * 64 / 2];            // [t][nt ^ (t&7)][q] -> {c_j, c_j+1, s_j, s_j+1}
   alignas(16) unsigned char qrot[NSLOT][ST_TOK / QSUB][HP * Q_PITCH];
-  alignas(16) StageMeta meta[MSLOT];
-  alignas(16) StageHdr hdr[NSLOT];
+  alignas(16) StageMeta meta[2][MSLOT];
+  alignas(16) StageHdr hdr[2][NSLOT];
   alignas(16) float merge[NCW][HP][PART_STRIDE];
   alignas(16) float knorm_w[D];
   alignas(16) unsigned char zero_chunk[16];
-  alignas(8) unsigned long long full_bar[NSLOT];
+  alignas(8) unsigned long long full_bar[2][NSLOT];   // [0] K bytes + rotated queries, [1] V bytes
   alignas(8) unsigned long long empty_bar[NSLOT];
   int prefix[MAX_BATCH + 1];
-  int ring_start[NSLOT];
+  int ring_start[2][NSLOT];
   int abort_flag;
 };
 
@@ -102,14 +96,20 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false (and raises the CTA's abort flag) instead of spinning forever.
+// Bounded wait for a whole warp: returns false (and raises the CTA's abort flag) instead of spinning forever.
+// Only lane 0 polls the barrier -- hundreds of threads polling would compete with the async copies for the
+// shared-memory barrier unit -- and the result (with lane 0's acquire) is handed to the warp by the shuffle.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
-    if (mbar_test(bar, parity)) return true;
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  int ok = 0;
+  if ((threadIdx.x & 31) == 0) {
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+      if (mbar_test(bar, parity)) { ok = 1; break; }
+      if ((it & 1023u) == 1023u && *abort_flag) break;
+      if (it + 1 == SPIN_LIMIT) *abort_flag = 1;
+    }
   }
-  *abort_flag = 1;
-  return false;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -118,6 +118,9 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 }
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -217,7 +220,7 @@ __host__ __device__ constexpr size_t ws_header_bytes() { return (sizeof(WsHeader
 
 // ------------------------------------------------------------------ the kernel
 template <typename T, bool FUSED, bool KNORM>
-__global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p, float log_theta, int n_cta) {
+__global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p, float log_theta, int n_cta, int meta16) {
   extern __shared__ unsigned char smem_raw[];
   SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
 
@@ -246,7 +249,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       sm.prefix[0] = 0;
       sm.abort_flag = 0;
       for (int s = 0; s < NSLOT; ++s) {
-        mbar_init(smem_u32(&sm.full_bar[s]), 2);               // loader (with tx bytes) + rotator
+        mbar_init(smem_u32(&sm.full_bar[0][s]), 2);            // K loader (with tx bytes) + rotator
+        mbar_init(smem_u32(&sm.full_bar[1][s]), 1);            // V loader (with tx bytes)
         mbar_init(smem_u32(&sm.empty_bar[s]), GRP_PER_STAGE);  // one arrival per 16-token group
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -382,48 +386,62 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.full_bar[slot]));
+      if (lane == 0) mbar_arrive(smem_u32(&sm.full_bar[0][slot]));
     }
     return;
   }
 
-  if (warp == NCW + 1) {
-    // =========================== loader warp ===========================
-    // Per stage: copy the raw lens/offs slices into a staging slot (cp.async, PD stages ahead), read the
-    // stage's first and one-past-last arena offsets from them (rows are gap-free, so the stage is one
-    // contiguous byte range per side), take ring space, and issue the two bulk copies.
-    auto prefetch = [&](int c, int row_hint) {
+  if (warp > NCW) {
+    // =========================== loader warps (one per side) ===========================
+    // Per stage: copy the side's raw lens/offs slices into a staging slot (cp.async, PD stages ahead), read
+    // the stage's first and one-past-last arena offsets from them (rows are gap-free, so the stage is one
+    // contiguous byte range), take ring space, and issue the bulk copy in two halves from two lanes.
+    const int side = warp - (NCW + 1);
+    const dkv_side& sd = side ? p.v : p.k;
+    unsigned char* const ring = sm.ring[side];
+    // per-row facts are cached and refreshed only when the stage sequence enters another batch row
+    struct RowInfo { int row, arena, tokens, first_unit; };
+    auto enter_row = [&](RowInfo& ri, int u) {
+      while (u >= sm.prefix[ri.row + 1]) ++ri.row;
+      const int b = p.batch_index ? p.batch_index[ri.row] : ri.row;
+      ri.arena = b * p.arenas_per_batch + g;
+      ri.tokens = row_tokens(p, ri.row);
+      ri.first_unit = sm.prefix[ri.row];
+    };
+    RowInfo pre{row0, 0, 0, 0}, cur{row0, 0, 0, 0};
+    int pre_end = -1, cur_end = -1;   // first unit past the cached row
+    auto prefetch = [&](int c) {
       if (c < n_stages) {
         const int u = u_begin + c;
-        int i = row_hint;
-        while (u >= sm.prefix[i + 1]) ++i;
-        const int b = p.batch_index ? p.batch_index[i] : i;
-        const int a = b * p.arenas_per_batch + g;
-        const int s0 = (u - sm.prefix[i]) * ST_TOK;
-        const int S_i = row_tokens(p, i);
-        StageMeta& dst = sm.meta[c % MSLOT];
-        const int32_t* lk = p.k.lens + (size_t)a * p.k.lens_stride_a + s0;
-        const int32_t* lv = p.v.lens + (size_t)a * p.v.lens_stride_a + s0;
-        const int32_t* ok = p.k.offs + (size_t)a * p.k.offs_stride_a + s0;
-        const int32_t* ov = p.v.offs + (size_t)a * p.v.offs_stride_a + s0;
+        if (u >= pre_end) { enter_row(pre, u); pre_end = sm.prefix[pre.row + 1]; }
+        const int s0 = (u - pre.first_unit) * ST_TOK;
+        StageMeta& dst = sm.meta[side][c % MSLOT];
+        const int32_t* ls = sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0;
+        const int32_t* os = sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0;
+        const int left = pre.tokens - s0;                 // tokens of the row from s0 on (> 0)
+        if (meta16) {
+          // 16-byte copies with zero fill past the row's last token (never reads beyond it)
+          const int t = lane * 4;
+          const int nbytes = min(max(left - t, 0), 4) * 4;
+          cp_async16_zfill(smem_u32(&dst.lens[t]), nbytes ? (const void*)(ls + t) : (const void*)ls, nbytes);
+          cp_async16_zfill(smem_u32(&dst.offs[t]), nbytes ? (const void*)(os + t) : (const void*)os, nbytes);
+        } else {
 #pragma unroll
-        for (int hh = 0; hh < ST_TOK / 32; ++hh) {
-          const int t = lane + 32 * hh;
-          if (s0 + t < S_i) {
-            cp_async4(smem_u32(&dst.lens_k[t]), lk + t);
-            cp_async4(smem_u32(&dst.lens_v[t]), lv + t);
-            cp_async4(smem_u32(&dst.offs_k[t]), ok + t);
-            cp_async4(smem_u32(&dst.offs_v[t]), ov + t);
-          } else {
-            dst.lens_k[t] = 0; dst.lens_v[t] = 0; dst.offs_k[t] = 0; dst.offs_v[t] = 0;
+          for (int hh = 0; hh < ST_TOK / 32; ++hh) {
+            const int t = lane + 32 * hh;
+            if (t < left) {
+              cp_async4(smem_u32(&dst.lens[t]), ls + t);
+              cp_async4(smem_u32(&dst.offs[t]), os + t);
+            } else {
+              dst.lens[t] = 0; dst.offs[t] = 0;
+            }
           }
         }
       }
       cp_async_commit();
     };
-    for (int c = 0; c < PD; ++c) prefetch(c, row0);
+    for (int c = 0; c < PD; ++c) prefetch(c);
 
-    int row = row0;
     int head = 0;         // ring allocation cursor (state is kept identical on all lanes)
     int oldest = 0;       // oldest stage whose ring bytes are still owned by consumers
     bool wrapped = false;
@@ -431,10 +449,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     auto release_oldest = [&](int c) -> bool {
       const bool done = mbar_wait(smem_u32(&sm.empty_bar[oldest % NSLOT]), (uint32_t)((oldest / NSLOT) & 1), abort_flag);
       if (!done) return false;
-      const int old_start = sm.ring_start[oldest % NSLOT];
+      const int old_start = sm.ring_start[side][oldest % NSLOT];
       ++oldest;
       if (oldest < c) {
-        const int new_start = sm.ring_start[oldest % NSLOT];
+        const int new_start = sm.ring_start[side][oldest % NSLOT];
         if (new_start < old_start) wrapped = false;
       } else {
         head = 0;
@@ -447,34 +465,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       // the stage that last used this slot (and the staging slot the next prefetch overwrites) must be done
       while (ok && oldest <= c - NSLOT) ok = release_oldest(c);
       if (!ok) break;
-      prefetch(c + PD, row);
+      prefetch(c + PD);
       cp_async_wait<PD>();
       __syncwarp();
       const int u = u_begin + c;
-      while (u >= sm.prefix[row + 1]) ++row;
-      const int b = p.batch_index ? p.batch_index[row] : row;
-      const int a = b * p.arenas_per_batch + g;
-      const int s0 = (u - sm.prefix[row]) * ST_TOK;
-      const int n_tok = min(ST_TOK, row_tokens(p, row) - s0);
-      const StageMeta& mt = sm.meta[c % MSLOT];
-      const int startK = mt.offs_k[0], startV = mt.offs_v[0];
-      const int endK = mt.offs_k[n_tok - 1] + mt.lens_k[n_tok - 1];
-      const int endV = mt.offs_v[n_tok - 1] + mt.lens_v[n_tok - 1];
-      int totK = endK - startK, totV = endV - startV;
-      // the byte ranges must be 16-byte aligned, inside the arena row and no larger than a full stage
-      const bool bad = ((startK | startV | endK | endV) & 7) != 0 || startK < 0 || startV < 0 || totK < 0 ||
-                       totV < 0 || totK > ST_TOK * 128 || totV > ST_TOK * 128 ||
-                       (int64_t)endK > p.k.flat_stride || (int64_t)endV > p.v.flat_stride;
+      if (u >= cur_end) { enter_row(cur, u); cur_end = sm.prefix[cur.row + 1]; }
+      const int s0 = (u - cur.first_unit) * ST_TOK;
+      const int n_tok = min(ST_TOK, cur.tokens - s0);
+      const StageMeta& mt = sm.meta[side][c % MSLOT];
+      const int start_el = mt.offs[0];
+      const int end_el = mt.offs[n_tok - 1] + mt.lens[n_tok - 1];
+      int tot = end_el - start_el;
+      // the byte range must be 16-byte aligned, inside the arena row and no larger than a full stage
+      const bool bad = ((start_el | end_el) & 7) != 0 || start_el < 0 || tot < 0 || tot > ST_TOK * 128 ||
+                       (int64_t)end_el > sd.flat_stride;
       if (bad) {
         if (lane == 0) set_status(p.status, DKV_ST_BAD_LENGTH);
-        totK = 0; totV = 0;     // consumers see an empty stage and skip its tokens
+        tot = 0;     // consumers see an empty stage and skip its tokens
       }
-      const int bytesK = totK * 2, bytesV = totV * 2, need = bytesK + bytesV;
+      const int need = tot * 2;
 
       int start = 0;
       while (ok) {
         if (oldest == c) { start = 0; head = 0; wrapped = false; break; }
-        const int tail = sm.ring_start[oldest % NSLOT];
+        const int tail = sm.ring_start[side][oldest % NSLOT];
         if (!wrapped) {
           if (head + need <= RING_BYTES) { start = head; break; }
           if (need <= tail) { start = 0; wrapped = true; break; }
@@ -486,34 +500,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       if (!ok) break;
       head = start + need;
       __syncwarp();
-      const uint32_t bar = smem_u32(&sm.full_bar[slot]);
-      const uint32_t kbase = smem_u32(sm.ring + start), vbase = kbase + (uint32_t)bytesK;
-      if (lane == 0) {
-        sm.ring_start[slot] = start;
+      const uint32_t bar = smem_u32(&sm.full_bar[side][slot]);
+      const uint32_t base = smem_u32(ring + start);
+      if (lane == 2) {
+        sm.ring_start[side][slot] = start;
         StageHdr h;
-        h.kbase = kbase;
-        h.vbase = vbase;
-        h.n_tok = n_tok;
-        h.start_k = startK; h.start_v = startV;
-        h.elems_k = totK; h.elems_v = totV;
-        h.pad = 0;
-        sm.hdr[slot] = h;
-        mbar_arrive_expect_tx(bar, (uint32_t)need);
-      }
-      // A thread sustains only a few bulk copies per microsecond, so the stage's two byte ranges are cut in
-      // halves and issued by four lanes (side = lane & 1, half = lane >> 1); all complete on the same barrier.
-      if (lane < 4) {
-        const int side = lane & 1, half = lane >> 1;
-        const int bytes = side ? bytesV : bytesK;
-        const int first = (bytes / 2) & ~15;                 // 16-byte aligned split point
-        const int off = half ? first : 0, len = half ? bytes - first : first;
-        const T* src = side ? reinterpret_cast<const T*>(p.v.flat) + (size_t)a * p.v.flat_stride + startV
-                            : reinterpret_cast<const T*>(p.k.flat) + (size_t)a * p.k.flat_stride + startK;
-        if (len > 0)
-          bulk_g2s((side ? vbase : kbase) + (uint32_t)off, reinterpret_cast<const unsigned char*>(src) + off,
-                   (uint32_t)len, bar);
+        h.base = base; h.n_tok = n_tok; h.start = start_el; h.elems = tot;
+        sm.hdr[side][slot] = h;
       }
       __syncwarp();
+      if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)need);
+      // a thread sustains only a few bulk copies per microsecond: the range is cut in two 16-byte aligned
+      // halves issued by two lanes; both complete on the same barrier
+      if (lane < 2) {
+        const int first = (need / 2) & ~15;
+        const int off = lane ? first : 0, len = lane ? need - first : first;
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(
+            reinterpret_cast<const T*>(sd.flat) + (size_t)cur.arena * sd.flat_stride + start_el);
+        if (len > 0) bulk_g2s(base + (uint32_t)off, src + off, (uint32_t)len, bar);
+      }
     }
     cp_async_wait<0>();
     if (!ok && lane == 0) set_status(p.status, DKV_ST_OVERFLOW);
@@ -541,33 +546,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const int c = grp / GRP_PER_STAGE, gi = grp % GRP_PER_STAGE;
       const int slot = c % NSLOT;
       if (*abort_flag) continue;
-      if (!mbar_wait(smem_u32(&sm.full_bar[slot]), (uint32_t)((c / NSLOT) & 1), abort_flag)) continue;
-      const StageHdr hdr = sm.hdr[slot];
-      const StageMeta& mt = sm.meta[c % MSLOT];
-      const int tok = gi * 16 + (lane & 15);     // lanes 16..31 mirror lanes 0..15
-      int klen = 0, vlen = 0;
-      uint32_t koff = 0u, voff = 0u;             // 16-byte chunks from the stage's K / V base
-      if (tok < hdr.n_tok) {
-        klen = mt.lens_k[tok];
-        vlen = mt.lens_v[tok];
-        const int ko = mt.offs_k[tok] - hdr.start_k, vo = mt.offs_v[tok] - hdr.start_v;   // elements
-        const bool bad_k = ((klen | ko) & 7) != 0 || klen < 0 || klen > R || ko < 0 || ko + klen > hdr.elems_k;
-        const bool bad_v = ((vlen | vo) & 7) != 0 || vlen < 0 || vlen > R || vo < 0 || vo + vlen > hdr.elems_v;
-        if (bad_k || bad_v) {   // breaks the layout contract: the token is dropped and the call flagged
-          set_status(p.status, DKV_ST_BAD_LENGTH);
-          if (bad_k) klen = 0;
-          vlen = 0;
+      const uint32_t phase = (uint32_t)((c / NSLOT) & 1);
+      if (!mbar_wait(smem_u32(&sm.full_bar[0][slot]), phase, abort_flag)) continue;
+      const StageHdr hdr = sm.hdr[0][slot];
+      int klen = 0;
+      uint32_t koff = 0u;                         // 16-byte chunks from the stage's K base
+      {
+        const StageMeta& mt = sm.meta[0][c % MSLOT];
+        const int tok = gi * 16 + (lane & 15);    // lanes 16..31 mirror lanes 0..15
+        if (tok < hdr.n_tok) {
+          klen = mt.lens[tok];
+          const int ko = mt.offs[tok] - hdr.start;   // elements
+          if (((klen | ko) & 7) != 0 || klen < 0 || klen > R || ko < 0 || ko + klen > hdr.elems) {
+            set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
+            klen = 0;
+          }
+          koff = (uint32_t)ko >> 3;
         }
-        koff = (uint32_t)ko >> 3;
-        voff = (uint32_t)vo >> 3;
       }
       const uint32_t valid = __ballot_sync(0xffffffffu, klen > 0) & 0xffffu;
       if (valid != 0u) {
         const int kmax = __reduce_max_sync(0xffffffffu, klen);
-        const int vmax = __reduce_max_sync(0xffffffffu, vlen);
         // ---------------- K = X . Bk ----------------
         float acc[16][4];
-        const uint32_t krow = hdr.kbase + koff * 16u;
+        const uint32_t krow = hdr.base + koff * 16u;
         const int cpar16 = lane >> 4;
         uint32_t a[4];
         ldsm_x4(a, (cpar16 * 8 < klen) ? krow + cpar16 * 16 : zero_addr);
@@ -694,11 +696,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           for (int i = 0; i < 8; ++i) { oacc[i][0] *= al0; oacc[i][1] *= al1; oacc[i][2] *= al0; oacc[i][3] *= al1; }
         }
         // ---------------- O^T[r x heads] += XV^T . P ----------------
-        {
-          const int tv = (lane & 7) + 8 * (lane >> 4);
-          const uint32_t voff_t = __shfl_sync(0xffffffffu, voff, tv);
-          const int vlen_t = __shfl_sync(0xffffffffu, vlen, tv);
-          const uint32_t vrow = hdr.vbase + voff_t * 16u;
+        if (mbar_wait(smem_u32(&sm.full_bar[1][slot]), phase, abort_flag)) {
+          const StageHdr hv = sm.hdr[1][slot];
+          const StageMeta& mv = sm.meta[1][c % MSLOT];
+          const int tv = gi * 16 + (lane & 7) + 8 * (lane >> 4);   // token whose row this lane addresses
+          int vlen_t = 0;
+          uint32_t vrow = zero_addr;
+          if (tv < hv.n_tok) {
+            vlen_t = mv.lens[tv];
+            const int vo = mv.offs[tv] - hv.start;
+            if (((vlen_t | vo) & 7) != 0 || vlen_t < 0 || vlen_t > R || vo < 0 || vo + vlen_t > hv.elems) {
+              set_status(p.status, DKV_ST_BAD_LENGTH);
+              vlen_t = 0;
+            }
+            vrow = hv.base + ((uint32_t)vo >> 3) * 16u;
+          }
+          const int vmax = __reduce_max_sync(0xffffffffu, vlen_t);
           const int cpar = (lane >> 3) & 1;
           uint32_t va[8][4];
 #pragma unroll
@@ -713,6 +726,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
             if (mt * 16 < vmax) Mma<T>::run(oacc[mt], va[mt][0], va[mt][1], va[mt][2], va[mt][3], pb0, pb1);
           }
         }
+      } else {
+        // nothing to do for this group, but its V bytes must have landed before the slot is handed back
+        mbar_wait(smem_u32(&sm.full_bar[1][slot]), phase, abort_flag);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sm.empty_bar[slot]));
@@ -936,15 +952,20 @@ static int launch_mma(const dkv_attn_args* a, int n_cta) {
   const float log_theta = (float)log((double)a->theta);
   const size_t smem = smem_bytes();
   dim3 grid(FUSED ? a->batch : n_cta, a->n_basis_groups);
+  // metadata rows that start on 16-byte boundaries are staged with 16-byte async copies
+  auto al16 = [](const dkv_side& s) {
+    return (((uintptr_t)s.lens | (uintptr_t)s.offs) & 15) == 0 && (s.lens_stride_a & 3) == 0 && (s.offs_stride_a & 3) == 0;
+  };
+  const int meta16 = al16(a->k) && al16(a->v) ? 1 : 0;
   cudaError_t e;
   if (a->k_norm_weight) {
     auto kern = mma_decode_kernel<T, FUSED, true>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta);
+    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta, meta16);
   } else {
     auto kern = mma_decode_kernel<T, FUSED, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta);
+    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta, meta16);
   }
   DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
   DKV_CHECK_LAUNCH();

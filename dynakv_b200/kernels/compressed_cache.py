@@ -35,6 +35,11 @@ def _round8(n: int) -> int:
     return (int(n) + 7) // 8 * 8
 
 
+def _round4(n: int) -> int:
+    # metadata rows that start on 16-byte boundaries can be staged with 16-byte async copies
+    return (int(n) + 3) // 4 * 4
+
+
 def simple_decompress(flat_values: torch.Tensor, lengths: torch.Tensor, max_dim: int,
                       offsets: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Ragged -> dense zero-padded [rows, S, max_dim].
@@ -140,8 +145,8 @@ class CustomDynamicCache:
     def _new_state(rows, flat_cap, seq_cap, dtype, device):
         return [
             torch.zeros((rows, max(flat_cap, 8)), dtype=dtype, device=device),
-            torch.zeros((rows, max(seq_cap, 1)), dtype=torch.int32, device=device),
-            torch.zeros((rows, max(seq_cap, 1)), dtype=torch.int32, device=device),
+            torch.zeros((rows, _round4(max(seq_cap, 1))), dtype=torch.int32, device=device),
+            torch.zeros((rows, _round4(max(seq_cap, 1))), dtype=torch.int32, device=device),
             torch.zeros(rows, dtype=torch.int32, device=device),
             0,
             [0] * rows,
@@ -152,7 +157,7 @@ class CustomDynamicCache:
         flat_buf, lens_buf, offs_buf = cache[0], cache[1], cache[2]
         if seq_cap > lens_buf.shape[1]:
             for i in (1, 2):
-                new = cache[i].new_zeros(cache[i].shape[0], seq_cap)
+                new = cache[i].new_zeros(cache[i].shape[0], _round4(seq_cap))
                 new[:, : cache[i].shape[1]].copy_(cache[i])
                 cache[i] = new
         if flat_cap > flat_buf.shape[1]:

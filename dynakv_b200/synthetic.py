@@ -66,7 +66,7 @@ def ragged_side(lens: torch.Tensor, gen: torch.Generator, dtype, flat_capacity: 
     tot = incl[:, -1] if S > 0 else torch.zeros(rows, dtype=torch.int64, device=dev)
     cap = int(tot.max().item()) if rows and S else 0
     cap = max((max(cap, flat_capacity or 0) + 7) // 8 * 8, 8)
-    scap = max(seq_capacity or S, S, 1)
+    scap = (max(seq_capacity or S, S, 1) + 3) // 4 * 4
     flat = torch.zeros((rows, cap), dtype=dtype, device=dev)
     sigma = torch.exp(-torch.arange(RANK, dtype=torch.float32, device=dev) / 32.0)
     tot_host = tot.cpu().tolist()

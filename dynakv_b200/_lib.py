@@ -21,7 +21,7 @@ _DTYPES = {torch.float32: DKV_F32, torch.float16: DKV_F16, torch.bfloat16: DKV_B
 
 EXPORTS = (
     "dkv_version", "dkv_last_error", "dkv_fused_decode", "dkv_split_workspace_bytes", "dkv_split_decode",
-    "dkv_split_combine", "dkv_two_stage_decode", "dkv_scores", "dkv_softmax_v", "dkv_append_decode",
+    "dkv_split_combine", "dkv_two_stage_decode", "dkv_two_stage_decode_noalloc", "dkv_scores", "dkv_softmax_v", "dkv_append_decode",
     "dkv_pack_bulk", "dkv_decompress",
 )
 
@@ -88,7 +88,8 @@ def load() -> C.CDLL:
     lib = C.CDLL(LIB_PATH)
     lib.dkv_version.restype = C.c_int
     lib.dkv_last_error.restype = C.c_char_p
-    for name in ("dkv_fused_decode", "dkv_split_decode", "dkv_split_combine", "dkv_two_stage_decode", "dkv_scores"):
+    for name in ("dkv_fused_decode", "dkv_split_decode", "dkv_split_combine", "dkv_two_stage_decode",
+                 "dkv_two_stage_decode_noalloc", "dkv_scores"):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(AttnArgs)]
         fn.restype = C.c_int

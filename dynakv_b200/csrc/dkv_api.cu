@@ -35,6 +35,7 @@ size_t mma_split_workspace_bytes(const dkv_attn_args* a);
 int mma_fused(const dkv_attn_args* a);
 int mma_split(const dkv_attn_args* a);
 int mma_combine(const dkv_attn_args* a);
+int mma_two_stage_noalloc(const dkv_attn_args* a);
 
 }  // namespace dkv
 
@@ -75,4 +76,9 @@ extern "C" int dkv_two_stage_decode(const dkv_attn_args* a) {
   if (!mma_path_ok(a)) return generic_attention(a);
   if (int rc = mma_split(a)) return rc;
   return mma_combine(a);
+}
+
+extern "C" int dkv_two_stage_decode_noalloc(const dkv_attn_args* a) {
+  if (int rc = check_attn_args(a, "dkv_two_stage_decode_noalloc", true, true, true)) return rc;
+  return mma_two_stage_noalloc(a);
 }

@@ -997,4 +997,50 @@ int mma_combine(const dkv_attn_args* a) {
   return DKV_OK;
 }
 
+// ---------------------------------------------------------------- entry point that allocates nothing
+// Some hosts of this library may not create device allocations at all: a serving process that has handed
+// every byte of HBM to its own pool at start-up, a plugin that runs inside someone else's captured or
+// real-time section, or a sandbox that forbids cudaMalloc after initialisation.  For them the split path's
+// partial-result scratch lives in this fixed array, which is part of the loaded module: every GPU that
+// loads the library holds these 2 MiB until the process exits.
+constexpr size_t NOALLOC_SCRATCH_BYTES = 2u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` is only a stand-in symbol, not a device address: the address is asked
+// from the runtime once per device, with that device current, and kept here.
+static void* g_noalloc_ptr[64];
+
+static int noalloc_scratch(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  DKV_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, DKV_E_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    DKV_REQUIRE(e == cudaSuccess && ptr != nullptr, DKV_E_CUDA, "cudaGetSymbolAddress(scratch) failed: %s",
+                cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return DKV_OK;
+}
+
+int mma_two_stage_noalloc(const dkv_attn_args* a) {
+  DKV_REQUIRE(mma_path_ok(a), DKV_E_ARG,
+              "dkv_two_stage_decode_noalloc: only the split tensor-core path uses scratch; the cache must have "
+              "16-bit elements, per-KV-head arenas, rank <= 128 and lengths declared as multiples of 8");
+  const size_t need = mma_split_workspace_bytes(a);
+  DKV_REQUIRE(need <= NOALLOC_SCRATCH_BYTES, DKV_E_LIMIT,
+              "dkv_two_stage_decode_noalloc: this call needs %zu bytes of scratch, the built-in array holds %zu "
+              "(reduce the batch per call or use dkv_two_stage_decode with a caller workspace)",
+              need, (size_t)NOALLOC_SCRATCH_BYTES);
+  dkv_attn_args b = *a;
+  void* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  b.workspace = scratch;
+  b.workspace_bytes = NOALLOC_SCRATCH_BYTES;
+  if (int rc = mma_split(&b)) return rc;
+  return mma_combine(&b);
+}
+
 }  // namespace dkv

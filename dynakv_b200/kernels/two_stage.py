@@ -32,6 +32,23 @@ def two_stage_attention(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta
     return out
 
 
+def two_stage_attention_noalloc(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta, *, out: torch.Tensor,
+                                seq_lens: Optional[torch.Tensor] = None, batch_index: Optional[torch.Tensor] = None,
+                                k_norm_weight: Optional[torch.Tensor] = None, k_norm_eps: float = 1e-6,
+                                len_multiple: int = 8):
+    """``two_stage_attention`` for processes that must not allocate device memory while serving: the
+    caller passes the output tensor, and the split partials go to a fixed 2 MiB array inside the library
+    instead of a torch workspace.  Raises when the call needs more scratch than that (large batches) or when
+    the cache does not qualify for the split tensor-core path.  Calls on one device must not overlap."""
+    q3 = q.squeeze(2) if q.dim() == 4 else q
+    args, keep = build_attn_args(q3, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta, out=out,
+                                 seq_lens=seq_lens, batch_index=batch_index, k_norm_weight=k_norm_weight,
+                                 k_norm_eps=k_norm_eps, len_multiple=len_multiple, need_workspace=False)
+    _lib.check(_lib.load().dkv_two_stage_decode_noalloc(C.byref(args)), "dkv_two_stage_decode_noalloc")
+    del keep
+    return out
+
+
 def abx_sparse(a: torch.Tensor, b: torch.Tensor, x_flat: torch.Tensor, l_vec: torch.Tensor,
                offsets: torch.Tensor = None, theta: float = 10000.0) -> torch.Tensor:
     """Scaled scores [B, Hq, S] in a's dtype; a = rotated queries [B,Hq,D], b = K basis [groups,R,D]."""

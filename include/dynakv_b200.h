@@ -109,6 +109,22 @@ int dkv_split_decode(const dkv_attn_args* a);
 int dkv_split_combine(const dkv_attn_args* a);
 int dkv_two_stage_decode(const dkv_attn_args* a);
 
+/* Long-cache path for callers that cannot allocate device memory.  (No counterpart in the reference.)
+ * Same inputs, outputs and results as dkv_two_stage_decode on a cache that qualifies for the split
+ * tensor-core path, but `workspace` / `workspace_bytes` are ignored: the per-split partial results go to a
+ * 2 MiB array built into the library (each GPU that loads the library holds it until the process ends).
+ * Meant for hosts that gave all device memory to their own pool at start-up, or that call from a context
+ * where cudaMalloc is forbidden; it calls no allocating routine of CUDA or any library.
+ *  - DKV_E_LIMIT when the call needs more scratch than the array holds (the message gives both sizes):
+ *    roughly groups * (batch + SMs/groups) * 2080 bytes, i.e. about 100 batch rows with 8 KV heads on a 148-SM GPU;
+ *    DKV_E_ARG when the cache does not qualify for the split path (nothing is computed).
+ *  - The first call on a device looks the array's address up (cudaGetSymbolAddress) and sets the
+ *    kernel's shared-memory attribute; make that first call outside any stream capture.
+ *  - All calls on a device share the array.  Nothing in it has to be cleared between calls (every record
+ *    that is read was written by the same call), but two calls that overlap on the GPU -- different
+ *    streams, or graph branches -- race on it: keep calls on one device ordered. */
+int dkv_two_stage_decode_noalloc(const dkv_attn_args* a);
+
 /* Stage 1 of the reference's two-stage path as a standalone op: scaled scores [batch, Hq, S] in the
  * query dtype, tokens of length 0 get -1e4*scale. Replaces abx_sparse (two_stage.py:159-189).
  * `out` is the score tensor; out_stride_b/out_stride_h are its strides, S contiguous. */

@@ -29,8 +29,8 @@
 namespace dkv {
 
 constexpr int D = 128;
-constexpr int NCW = 9;                 // consumer warps; warp NCW = query rotator, NCW+1 / NCW+2 = K / V loader
-constexpr int NTHREADS = (NCW + 3) * 32;   // 12 warps = 3 per SM sub-partition
+constexpr int NCW = 13;                // consumer warps; warp NCW = query rotator, NCW+1 / NCW+2 = K / V loader
+constexpr int NTHREADS = (NCW + 3) * 32;   // 16 warps = 4 per SM sub-partition, 128 registers per thread
 constexpr int ST_TOK = 128;            // tokens per stage (one pair of bulk copies, one metadata block)
 constexpr int QSUB = 64;               // tokens per query-rotation sub-stage (extent of the local RoPE table)
 constexpr int GRP_PER_STAGE = ST_TOK / 16;  // 16-token groups, each handled by one consumer warp
@@ -567,110 +567,103 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const uint32_t valid = __ballot_sync(0xffffffffu, klen > 0) & 0xffffu;
       if (valid != 0u) {
         const int kmax = __reduce_max_sync(0xffffffffu, klen);
-        // ---------------- K = X . Bk ----------------
-        float acc[16][4];
+        // ---------------- K = X . Bk, RoPE, S = K' . Q~^T : two passes over half of the head dims ----------------
+        // Pass h reconstructs dims [32h, 32h+32) and their rotation partners [64+32h, 64+32h+32) (n-tiles
+        // 4h..4h+3 and 8+4h..8+4h+3), rotates them and adds their part of the score, so only 32 accumulator
+        // registers are live at a time (this is what lets 16 warps fit on the SM).
         const uint32_t krow = hdr.base + koff * 16u;
         const int cpar16 = lane >> 4;
-        uint32_t a[4];
-        ldsm_x4(a, (cpar16 * 8 < klen) ? krow + cpar16 * 16 : zero_addr);
-        // one k-step = 16 latent coefficients: basis fragments are fetched four ldmatrix at a time ahead of
-        // the eight MMAs that use them, and the next step's coefficient fragment is loaded meanwhile.
-        // The first step writes the accumulators (no zero fill), later steps add to them.
-        auto kstep = [&](int ks, auto first) {
-          uint32_t an[4] = {0u, 0u, 0u, 0u};
-          if ((ks + 1) * 16 < kmax) {
-            const int chunk = 2 * (ks + 1) + cpar16;
-            ldsm_x4(an, (chunk * 8 < klen) ? krow + chunk * 16 : zero_addr);
-          }
-          const uint32_t brow = basis_lane + ks * 16 * BASIS_PITCH;
+        const uint32_t qbase = smem_u32(sm.qrot[slot][gi / (QSUB / 16)]);
+        const int qr = lane & 7;   // ldmatrix rows 0..HP-1 = heads, the other rows read the zero chunk
+        const uint32_t qaddr = (qr < HP) ? qbase + qr * Q_PITCH + (lane >> 3) * 16 : zero_addr;
+        const int tA = (gi & (QSUB / 16 - 1)) * 16 + gq, tB = tA + 8;   // offsets inside the 64-token sub-stage
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+        float ss0 = 0.f, ss1 = 0.f;     // sum of squares of the two token rows (K-RMSNorm)
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
+        for (int hf = 0; hf < 2; ++hf) {
+          float acc[8][4];              // [0..3] = n-tiles 4hf+i (dims j), [4..7] = n-tiles 8+4hf+i (dims j+64)
+          uint32_t a[4];
+          ldsm_x4(a, (cpar16 * 8 < klen) ? krow + cpar16 * 16 : zero_addr);
+          // one k-step = 16 latent coefficients: the four basis ldmatrix of the pass are issued ahead of its
+          // eight MMAs and the next step's coefficient fragment is loaded meanwhile; the first step writes
+          // the accumulators (no zero fill), later steps add to them
+          auto kstep = [&](int ks, auto first) {
+            uint32_t an[4] = {0u, 0u, 0u, 0u};
+            if ((ks + 1) * 16 < kmax) {
+              const int chunk = 2 * (ks + 1) + cpar16;
+              ldsm_x4(an, (chunk * 8 < klen) ? krow + chunk * 16 : zero_addr);
+            }
+            const uint32_t brow = basis_lane + ks * 16 * BASIS_PITCH;
             uint32_t bb[4][4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) ldsm_x4_t_const(bb[j], brow + (half * 4 + j) * 32);
+            for (int j = 0; j < 4; ++j)   // n-tile pairs: 2hf, 2hf+1 (low dims) and 4+2hf, 4+2hf+1 (partners)
+              ldsm_x4_t_const(bb[j], brow + ((j >> 1) * 4 + 2 * hf + (j & 1)) * 32);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const int ntp = half * 4 + j;
               if (decltype(first)::value) {
-                Mma<T>::run0(acc[2 * ntp], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
-                Mma<T>::run0(acc[2 * ntp + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
+                Mma<T>::run0(acc[2 * j], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
+                Mma<T>::run0(acc[2 * j + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
               } else {
-                Mma<T>::run(acc[2 * ntp], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
-                Mma<T>::run(acc[2 * ntp + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
+                Mma<T>::run(acc[2 * j], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
+                Mma<T>::run(acc[2 * j + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
               }
             }
-          }
-          a[0] = an[0]; a[1] = an[1]; a[2] = an[2]; a[3] = an[3];
-        };
-        kstep(0, std::true_type{});
-        for (int ks = 1; ks * 16 < kmax; ++ks) kstep(ks, std::false_type{});
-        // ---------------- optional RMSNorm of K (Qwen3) ----------------
-        float rs0 = 1.f, rs1 = 1.f;
-        if (KNORM) {
-          float s0 = 0.f, s1 = 0.f;
+            a[0] = an[0]; a[1] = an[1]; a[2] = an[2]; a[3] = an[3];
+          };
+          kstep(0, std::true_type{});
+          for (int ks = 1; ks * 16 < kmax; ++ks) kstep(ks, std::false_type{});
+          if (KNORM) {
+            // RMSNorm of K (Qwen3): the weight is applied here, the per-token 1/rms scales the score at the end
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            s0 = fmaf(acc[i][0], acc[i][0], fmaf(acc[i][1], acc[i][1], s0));
-            s1 = fmaf(acc[i][2], acc[i][2], fmaf(acc[i][3], acc[i][3], s1));
+            for (int i = 0; i < 8; ++i) {
+              ss0 = fmaf(acc[i][0], acc[i][0], fmaf(acc[i][1], acc[i][1], ss0));
+              ss1 = fmaf(acc[i][2], acc[i][2], fmaf(acc[i][3], acc[i][3], ss1));
+              const int nt = (i >> 2) * 8 + 4 * hf + (i & 3);
+              const float2 w = *reinterpret_cast<const float2*>(&sm.knorm_w[8 * nt + 2 * qq]);
+              acc[i][0] *= w.x; acc[i][1] *= w.y; acc[i][2] *= w.x; acc[i][3] *= w.y;
+            }
           }
-          s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-          s1 += __shfl_xor_sync(0xffffffffu, s1, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-          rs0 = rsqrtf(s0 * (1.0f / D) + p.k_norm_eps);
-          rs1 = rsqrtf(s1 * (1.0f / D) + p.k_norm_eps);
+          // local RoPE on packed fp32 pairs, packed to 16-bit A fragments
+          uint32_t kl[4][2], kh[4][2];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float2 w = *reinterpret_cast<const float2*>(&sm.knorm_w[8 * i + 2 * qq]);
-            acc[i][0] *= w.x * rs0; acc[i][1] *= w.y * rs0;
-            acc[i][2] *= w.x * rs1; acc[i][3] *= w.y * rs1;
-          }
-        }
-        // ---------------- local RoPE (packed fp32 pairs), pack to 16-bit A fragments ----------------
-        uint32_t kb[16][2];
-        {
-          const int tA = (gi & (QSUB / 16 - 1)) * 16 + gq, tB = tA + 8;   // offset inside the 64-token sub-stage
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
+          for (int i = 0; i < 4; ++i) {
+            const int nt = 4 * hf + i;
             const float4 ta = trig4[(tA * 8 + (nt ^ (tA & 7))) * 4 + qq];   // {c_j, c_j+1, s_j, s_j+1}
             const float4 tb = trig4[(tB * 8 + (nt ^ (tB & 7))) * 4 + qq];
             {
-              const float2 lo = make_float2(acc[nt][0], acc[nt][1]), hi = make_float2(acc[nt + 8][0], acc[nt + 8][1]);
+              const float2 lo = make_float2(acc[i][0], acc[i][1]), hi = make_float2(acc[4 + i][0], acc[4 + i][1]);
               const float2 C = make_float2(ta.x, ta.y), S = make_float2(ta.z, ta.w);
               const float2 u = __fmul2_rn(hi, S);
               const float2 lo2 = __ffma2_rn(lo, C, make_float2(-u.x, -u.y));
               const float2 hi2 = __ffma2_rn(lo, S, __fmul2_rn(hi, C));
-              kb[nt][0] = Mma<T>::pack(lo2.x, lo2.y);
-              kb[nt + 8][0] = Mma<T>::pack(hi2.x, hi2.y);
+              kl[i][0] = Mma<T>::pack(lo2.x, lo2.y);
+              kh[i][0] = Mma<T>::pack(hi2.x, hi2.y);
             }
             {
-              const float2 lo = make_float2(acc[nt][2], acc[nt][3]), hi = make_float2(acc[nt + 8][2], acc[nt + 8][3]);
+              const float2 lo = make_float2(acc[i][2], acc[i][3]), hi = make_float2(acc[4 + i][2], acc[4 + i][3]);
               const float2 C = make_float2(tb.x, tb.y), S = make_float2(tb.z, tb.w);
               const float2 u = __fmul2_rn(hi, S);
               const float2 lo2 = __ffma2_rn(lo, C, make_float2(-u.x, -u.y));
               const float2 hi2 = __ffma2_rn(lo, S, __fmul2_rn(hi, C));
-              kb[nt][1] = Mma<T>::pack(lo2.x, lo2.y);
-              kb[nt + 8][1] = Mma<T>::pack(hi2.x, hi2.y);
+              kl[i][1] = Mma<T>::pack(lo2.x, lo2.y);
+              kh[i][1] = Mma<T>::pack(hi2.x, hi2.y);
             }
           }
+          // S[tokens x heads] += K'[:, these dims] . Q~^T : the rotated fragments are the A operand, the rotated
+          // queries the B operand.  16-dim steps 2hf, 2hf+1 (low dims) and 4+2hf, 4+2hf+1 (partners).
+          uint32_t ql[4], qh[4];
+          ldsm_x4(ql, (qr < HP) ? qaddr + hf * 64 : zero_addr);         // {step 2hf: dims 0-7, 8-15 ; step 2hf+1: ...}
+          ldsm_x4(qh, (qr < HP) ? qaddr + (2 + hf) * 64 : zero_addr);
+          Mma<T>::run(sacc, kl[0][0], kl[0][1], kl[1][0], kl[1][1], ql[0], ql[1]);
+          Mma<T>::run(sacc, kl[2][0], kl[2][1], kl[3][0], kl[3][1], ql[2], ql[3]);
+          Mma<T>::run(sacc, kh[0][0], kh[0][1], kh[1][0], kh[1][1], qh[0], qh[1]);
+          Mma<T>::run(sacc, kh[2][0], kh[2][1], kh[3][0], kh[3][1], qh[2], qh[3]);
         }
-        // ---------------- S[tokens x heads] = K' . Q~^T ----------------
-        // accumulator fragments of K' double as the A operand; the rotated queries are the B operand
-        float sacc[4];
-        {
-          // ldmatrix rows 0..HP-1 = heads, the other rows read the zero chunk
-          const uint32_t qbase = smem_u32(sm.qrot[slot][gi / (QSUB / 16)]);
-          const int qr = lane & 7;
-          const uint32_t qaddr = (qr < HP) ? qbase + qr * Q_PITCH + (lane >> 3) * 16 : zero_addr;
-          uint32_t qa[4][4];
-#pragma unroll
-          for (int kp = 0; kp < 4; ++kp)   // {d-step 2kp: dims 0-7, 8-15 ; d-step 2kp+1: dims 0-7, 8-15}
-            ldsm_x4(qa[kp], (qr < HP) ? qaddr + kp * 64 : zero_addr);
-          Mma<T>::run0(sacc, kb[0][0], kb[0][1], kb[1][0], kb[1][1], qa[0][0], qa[0][1]);
-          Mma<T>::run(sacc, kb[2][0], kb[2][1], kb[3][0], kb[3][1], qa[0][2], qa[0][3]);
-#pragma unroll
-          for (int kp = 1; kp < 4; ++kp) {
-            Mma<T>::run(sacc, kb[4 * kp][0], kb[4 * kp][1], kb[4 * kp + 1][0], kb[4 * kp + 1][1], qa[kp][0], qa[kp][1]);
-            Mma<T>::run(sacc, kb[4 * kp + 2][0], kb[4 * kp + 2][1], kb[4 * kp + 3][0], kb[4 * kp + 3][1], qa[kp][2], qa[kp][3]);
-          }
+        if (KNORM) {
+          ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+          ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+          const float rs0 = rsqrtf(ss0 * (1.0f / D) + p.k_norm_eps), rs1 = rsqrtf(ss1 * (1.0f / D) + p.k_norm_eps);
+          sacc[0] *= rs0; sacc[1] *= rs0; sacc[2] *= rs1; sacc[3] *= rs1;
         }
         // ---------------- online softmax (base 2) ----------------
         // this lane: tokens gq and gq+8, heads 2qq and 2qq+1; head maxima are reduced over the 8 token lanes

@@ -4,19 +4,19 @@
 //   * the long-cache split path: a persistent grid that partitions each KV head's token space
 //     evenly over CTAs and writes (m, l, latent accumulator) partials, merged by a combine kernel.
 //
-// Per CTA: one producer warp + 8 consumer warps.
-//   producer : reads the token lengths of a 64-token stage, scans them into byte offsets, allocates
-//              a byte range in a shared-memory ring and pulls the stage's contiguous K and V bytes
-//              with two bulk async copies (cp.async.bulk, mbarrier completion).  It also rotates the
-//              group's queries back by the stage's base position so consumers only apply a local
-//              (0..63) rotation to K.
-//   consumer : each warp owns a 16-token group of a stage:
-//              K  = X[16 x r] . Bk[r x 128]      mma.sync m16n8k16, X read with ldmatrix straight from
-//                                                the ragged bytes (zero chunk beyond a row's length)
-//              K' = RoPE_local(K)                 fp32 in registers, pairs (j, j+64) sit in one thread
-//              S^T= Q~[heads x 128] . K'^T        mma.sync, accumulator fragments reused as B operand
-//              online softmax (exp2, quad shuffles), P^T reused as B operand
-//              O^T[r x heads] += XV^T . P         mma.sync, XV read with ldmatrix.trans
+// Per CTA 16 warps work on 128-token stages:
+//   4 gather warps : copy each token's ragged coefficient row (16-byte cp.async, zero fill past the row's
+//                    length) into a K-major, unswizzled operand tile in shared memory;
+//   1 MMA warp     : K[128 x 128] = X[128 x 128] . Bk with eight tcgen05.mma (M=128, N=128, K=16), the
+//                    accumulator in tensor memory (two 128-column buffers), completion by tcgen05.commit;
+//   1 V loader     : the stage's V bytes are one contiguous range (rows are gap-free): cp.async.bulk into
+//                    a shared-memory ring, mbarrier transaction completion;
+//   1 rotator      : q~ = scale . R(-s0) q per 64-token sub-stage, so consumers rotate K only locally;
+//   8 consumers    : one 16-token group each per stage.  tcgen05.ld.16x256b brings the group's K rows into
+//                    registers in the mma.sync accumulator layout; RoPE in fp32 (pairs (j, j+64) sit in
+//                    one thread); S = K'.q~^T with mma.sync reusing the fragments as A operand; online
+//                    softmax (exp2, shuffles); O^T[r x heads] += XV^T . P with mma.sync, XV read by
+//                    ldmatrix.trans straight from the ragged V bytes.
 //
 // Reference math: src/dynakv/kernels/fused.py:28-142 (fused), two_stage.py:52-157,211-281 (two-stage;
 // the latent-space V accumulation with one up-projection at the end is two_stage.py:261-277).
@@ -29,23 +29,30 @@
 namespace dkv {
 
 constexpr int D = 128;
-constexpr int NCW = 13;                // consumer warps; warp NCW = query rotator, NCW+1 / NCW+2 = K / V loader
-constexpr int NTHREADS = (NCW + 3) * 32;   // 16 warps = 4 per SM sub-partition, 128 registers per thread
-constexpr int ST_TOK = 128;            // tokens per stage (one pair of bulk copies, one metadata block)
+constexpr int NCW = 8;                 // consumer warps (warp w owns TMEM lanes 32(w&3)+16(w>>2) .. +15)
+constexpr int W_ROT = 8;               // query rotator
+constexpr int W_VLOAD = 9;             // V loader
+constexpr int W_GATHER0 = 10;          // gather warps 10..13 (32 tokens of the stage each)
+constexpr int N_GATHER = 4;
+constexpr int W_MMA = 14;              // tcgen05.mma issuer, owns the tensor-memory allocation
+constexpr int NTHREADS = 16 * 32;      // 4 warps per SM sub-partition, 128 registers per thread
+constexpr int ST_TOK = 128;            // tokens per stage = rows of one UMMA
 constexpr int QSUB = 64;               // tokens per query-rotation sub-stage (extent of the local RoPE table)
-constexpr int GRP_PER_STAGE = ST_TOK / 16;  // 16-token groups, each handled by one consumer warp
-constexpr int NSLOT = 6;               // stages in flight
-constexpr int PD = 4;                  // loader prefetch distance for the stage metadata (stages)
+constexpr int GRP_PER_STAGE = ST_TOK / 16;  // 16-token groups, one per consumer warp
+constexpr int NSLOT = 4;               // stages in flight (metadata, rotated queries, V bytes)
+constexpr int PD = 4;                  // prefetch distance for the stage metadata (stages)
 constexpr int MSLOT = NSLOT + PD;      // metadata staging slots
-constexpr int BASIS_PITCH = 272;       // bytes per basis row in smem (256 + 16: conflict-free ldmatrix)
+constexpr int NBUF = 2;                // K operand tiles in shared memory = accumulator buffers in tensor memory
+constexpr int A_TILE_BYTES = ST_TOK * 128 * 2;   // 128 tokens x 128 coefficients, chunk-major (see gather)
+constexpr int TMEM_COLS = NBUF * 128;  // fp32 accumulator columns
 constexpr int Q_PITCH = 272;
 constexpr int HP = 4;                  // query heads per KV head supported by this kernel
-constexpr int RING_BYTES = 36 * 1024;  // per side; >= one worst-case stage (128 tokens x 256 B)
+constexpr int RING_BYTES = 36 * 1024;  // V ring; >= one worst-case stage (128 tokens x 256 B)
 constexpr int MAX_BATCH = 1024;
 constexpr int PART_STRIDE = 2 + 128;   // floats per (head) partial record: m, l, latent[128]
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
-struct __align__(16) StageHdr {   // one side (K or V) of one stage
+struct __align__(16) StageHdr {   // V side of one stage
   uint32_t base;    // shared-memory byte address of the stage's bytes
   int32_t n_tok;
   int32_t start;    // arena element offset of the stage's first coefficient
@@ -58,20 +65,27 @@ struct StageMeta {   // raw slices of one side's cache metadata for one stage, c
 };
 
 struct SmemLayout {
-  alignas(128) unsigned char ring[2][RING_BYTES];
-  alignas(16) unsigned char basis[128 * BASIS_PITCH];
+  alignas(1024) unsigned char a_tile[NBUF][A_TILE_BYTES];   // chunk c (8 coefficients) of token t at c*2048 + t*16
+  alignas(1024) unsigned char basis[128 * 256];             // Bk[r][d] at (r/8)*2048 + (d/8)*128 + (r%8)*16 + (d%8)*2
+  alignas(128) unsigned char ring[RING_BYTES];
   alignas(16) float4 trig[QSUB * 64 / 2];            // [t][nt ^ (t&7)][q] -> {c_j, c_j+1, s_j, s_j+1}
   alignas(16) unsigned char qrot[NSLOT][ST_TOK / QSUB][HP * Q_PITCH];
-  alignas(16) StageMeta meta[2][MSLOT];
-  alignas(16) StageHdr hdr[2][NSLOT];
+  alignas(16) StageMeta meta[2][MSLOT];              // [0] K side, [1] V side
+  alignas(16) StageHdr hdr[NSLOT];
   alignas(16) float merge[NCW][HP][PART_STRIDE];
   alignas(16) float knorm_w[D];
   alignas(16) unsigned char zero_chunk[16];
-  alignas(8) unsigned long long full_bar[2][NSLOT];   // [0] K bytes + rotated queries, [1] V bytes
-  alignas(8) unsigned long long empty_bar[NSLOT];
+  alignas(8) unsigned long long full_k[NSLOT];    // K metadata (4 gather warps) + rotated queries (rotator)
+  alignas(8) unsigned long long full_v[NSLOT];    // V bytes (loader arrive + transaction bytes)
+  alignas(8) unsigned long long empty_bar[NSLOT]; // 8 consumer groups done with the stage
+  alignas(8) unsigned long long a_full[NBUF];     // operand tile written (4 gather warps)
+  alignas(8) unsigned long long a_free[NBUF];     // operand tile consumed by the tensor core (commit)
+  alignas(8) unsigned long long t_ready[NBUF];    // accumulator buffer written (commit)
+  alignas(8) unsigned long long t_free[NBUF];     // accumulator buffer read out (8 consumer warps)
   int prefix[MAX_BATCH + 1];
-  int ring_start[2][NSLOT];
+  int ring_start[NSLOT];
   int abort_flag;
+  uint32_t tmem_base;
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -127,6 +141,45 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+// tcgen05 (5th generation tensor core) helpers ---------------------------------------------------------
+// Shared-memory matrix descriptor, no swizzle: start address, leading and stride byte offsets in 16-byte
+// units, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Two 16-row x 32-column fp32 blocks of tensor memory in the mma.sync accumulator layout:
+// v[i][0..3] = n-tile i {(row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)}, g = lane/4, q = lane%4;
+// v[0..3] from addr_lo, v[4..7] from addr_hi.  The wait is part of the same statement, so no register of
+// the result can be touched before the loads have landed.
+__device__ __forceinline__ void tmem_ld_2x_16x32(float (&v)[8][4], uint32_t addr_lo, uint32_t addr_hi) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%32];\n"
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%33];\n"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr_lo), "r"(addr_hi)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[i][j] = __uint_as_float(r[4 * i + j]);
+}
+
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -222,7 +275,7 @@ __host__ __device__ constexpr size_t ws_header_bytes() { return (sizeof(WsHeader
 template <typename T, bool FUSED, bool KNORM>
 __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p, float log_theta, int n_cta, int meta16) {
   extern __shared__ unsigned char smem_raw[];
-  SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+  SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = blockIdx.y;                        // KV head == basis group == arena within the batch row
@@ -249,9 +302,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       sm.prefix[0] = 0;
       sm.abort_flag = 0;
       for (int s = 0; s < NSLOT; ++s) {
-        mbar_init(smem_u32(&sm.full_bar[0][s]), 2);            // K loader (with tx bytes) + rotator
-        mbar_init(smem_u32(&sm.full_bar[1][s]), 1);            // V loader (with tx bytes)
+        mbar_init(smem_u32(&sm.full_k[s]), N_GATHER + 1);      // gather warps (metadata) + rotator
+        mbar_init(smem_u32(&sm.full_v[s]), 1);                 // V loader (with tx bytes)
         mbar_init(smem_u32(&sm.empty_bar[s]), GRP_PER_STAGE);  // one arrival per 16-token group
+      }
+      for (int s = 0; s < NBUF; ++s) {
+        mbar_init(smem_u32(&sm.a_full[s]), N_GATHER);
+        mbar_init(smem_u32(&sm.a_free[s]), 1);
+        mbar_init(smem_u32(&sm.t_ready[s]), 1);
+        mbar_init(smem_u32(&sm.t_free[s]), NCW);
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -289,13 +348,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 
   // ---- prologue B: basis and local-rotation table (only CTAs that have work) ---------------------
   {
-    // basis rows [R][128] -> smem with padded pitch; rows >= R are zero
+    // basis rows [R][128] -> the MN-major unswizzled operand layout of the tensor core: 8x8 core matrices,
+    // element (r, d) at (r/8)*2048 + (d/8)*128 + (r%8)*16 + (d%8)*2; rows >= R are zero
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.k_up) + (size_t)g * R * D);
     for (int e = tid; e < 128 * 16; e += NTHREADS) {
       const int r = e >> 4, c = e & 15;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (r < R) v = src[r * 16 + c];
-      *reinterpret_cast<uint4*>(sm.basis + r * BASIS_PITCH + c * 16) = v;
+      *reinterpret_cast<uint4*>(sm.basis + (r >> 3) * 2048 + c * 128 + (r & 7) * 16) = v;
+    }
+    if (warp == W_MMA) {   // tensor-memory columns for the two accumulator buffers
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                   "r"(TMEM_COLS));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     // local rotation table for offsets t = 0..63: angle = t * f_j, f_j = exp(-(2j/D) ln theta).
     // NTHREADS is a multiple of 64, so a thread keeps one j and steps t by NTHREADS/64: one exact
@@ -318,7 +383,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
     if (KNORM && tid < D) sm.knorm_w[tid] = p.k_norm_weight[tid];
   }
+  proxy_fence_async();     // the basis was written with ordinary stores and is read by the tensor core
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_base;
 
   // first batch row touched by this CTA
   int row0 = 0;
@@ -331,7 +400,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     row0 = FUSED ? (int)blockIdx.x : lo;
   }
 
-  if (warp == NCW) {
+  if (warp == W_ROT) {
     // =========================== query rotator warp ===========================
     // For every 64-token sub-stage with base position s0 it publishes q~ = scale * R(-s0) q for the
     // group's heads, so that q~ . R(t) k = q . R(s0 + t) k with the local offset t = 0..63.
@@ -386,19 +455,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.full_bar[0][slot]));
+      if (lane == 0) mbar_arrive(smem_u32(&sm.full_k[slot]));
     }
-    return;
   }
 
-  if (warp > NCW) {
-    // =========================== loader warps (one per side) ===========================
-    // Per stage: copy the side's raw lens/offs slices into a staging slot (cp.async, PD stages ahead), read
+  else if (warp == W_VLOAD) {
+    // =========================== V loader warp ===========================
+    // Per stage: copy the V side's raw lens/offs slices into a staging slot (cp.async, PD stages ahead), read
     // the stage's first and one-past-last arena offsets from them (rows are gap-free, so the stage is one
     // contiguous byte range), take ring space, and issue the bulk copy in two halves from two lanes.
-    const int side = warp - (NCW + 1);
-    const dkv_side& sd = side ? p.v : p.k;
-    unsigned char* const ring = sm.ring[side];
+    const dkv_side& sd = p.v;
+    unsigned char* const ring = sm.ring;
     // per-row facts are cached and refreshed only when the stage sequence enters another batch row
     struct RowInfo { int row, arena, tokens, first_unit; };
     auto enter_row = [&](RowInfo& ri, int u) {
@@ -415,7 +482,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         const int u = u_begin + c;
         if (u >= pre_end) { enter_row(pre, u); pre_end = sm.prefix[pre.row + 1]; }
         const int s0 = (u - pre.first_unit) * ST_TOK;
-        StageMeta& dst = sm.meta[side][c % MSLOT];
+        StageMeta& dst = sm.meta[1][c % MSLOT];
         const int32_t* ls = sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0;
         const int32_t* os = sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0;
         const int left = pre.tokens - s0;                 // tokens of the row from s0 on (> 0)
@@ -449,10 +516,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     auto release_oldest = [&](int c) -> bool {
       const bool done = mbar_wait(smem_u32(&sm.empty_bar[oldest % NSLOT]), (uint32_t)((oldest / NSLOT) & 1), abort_flag);
       if (!done) return false;
-      const int old_start = sm.ring_start[side][oldest % NSLOT];
+      const int old_start = sm.ring_start[oldest % NSLOT];
       ++oldest;
       if (oldest < c) {
-        const int new_start = sm.ring_start[side][oldest % NSLOT];
+        const int new_start = sm.ring_start[oldest % NSLOT];
         if (new_start < old_start) wrapped = false;
       } else {
         head = 0;
@@ -472,7 +539,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       if (u >= cur_end) { enter_row(cur, u); cur_end = sm.prefix[cur.row + 1]; }
       const int s0 = (u - cur.first_unit) * ST_TOK;
       const int n_tok = min(ST_TOK, cur.tokens - s0);
-      const StageMeta& mt = sm.meta[side][c % MSLOT];
+      const StageMeta& mt = sm.meta[1][c % MSLOT];
       const int start_el = mt.offs[0];
       const int end_el = mt.offs[n_tok - 1] + mt.lens[n_tok - 1];
       int tot = end_el - start_el;
@@ -488,7 +555,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       int start = 0;
       while (ok) {
         if (oldest == c) { start = 0; head = 0; wrapped = false; break; }
-        const int tail = sm.ring_start[side][oldest % NSLOT];
+        const int tail = sm.ring_start[oldest % NSLOT];
         if (!wrapped) {
           if (head + need <= RING_BYTES) { start = head; break; }
           if (need <= tail) { start = 0; wrapped = true; break; }
@@ -500,13 +567,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       if (!ok) break;
       head = start + need;
       __syncwarp();
-      const uint32_t bar = smem_u32(&sm.full_bar[side][slot]);
+      const uint32_t bar = smem_u32(&sm.full_v[slot]);
       const uint32_t base = smem_u32(ring + start);
       if (lane == 2) {
-        sm.ring_start[side][slot] = start;
+        sm.ring_start[slot] = start;
         StageHdr h;
         h.base = base; h.n_tok = n_tok; h.start = start_el; h.elems = tot;
-        sm.hdr[side][slot] = h;
+        sm.hdr[slot] = h;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)need);
@@ -522,19 +589,124 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
     cp_async_wait<0>();
     if (!ok && lane == 0) set_status(p.status, DKV_ST_OVERFLOW);
-    return;
   }
 
+  else if (warp >= W_GATHER0 && warp < W_GATHER0 + N_GATHER) {
+    // =========================== gather warps ===========================
+    // Lane l of gather warp j owns token 32j + l of every stage: it stages the token's length and offset
+    // (cp.async, PD stages ahead) and copies the token's coefficient row into the operand tile, one 16-byte
+    // chunk per cp.async, chunk c of token t at c*2048 + t*16; chunks past the row's length are zero-filled
+    // (source size 0), so the tensor core always multiplies a full 128 x 128 tile.
+    const int t = (warp - W_GATHER0) * 32 + lane;
+    const dkv_side& sd = p.k;
+    struct RowInfo { int row, arena, tokens, first_unit; };
+    auto enter_row = [&](RowInfo& ri, int u) {
+      while (u >= sm.prefix[ri.row + 1]) ++ri.row;
+      const int b = p.batch_index ? p.batch_index[ri.row] : ri.row;
+      ri.arena = b * p.arenas_per_batch + g;
+      ri.tokens = row_tokens(p, ri.row);
+      ri.first_unit = sm.prefix[ri.row];
+    };
+    RowInfo pre{row0, 0, 0, 0}, cur{row0, 0, 0, 0};
+    int pre_end = -1, cur_end = -1;
+    auto prefetch_meta = [&](int c) {   // no commit: the caller groups it with the stage's data copies
+      if (c < n_stages) {
+        const int u = u_begin + c;
+        if (u >= pre_end) { enter_row(pre, u); pre_end = sm.prefix[pre.row + 1]; }
+        const int s0 = (u - pre.first_unit) * ST_TOK;
+        StageMeta& dst = sm.meta[0][c % MSLOT];
+        if (s0 + t < pre.tokens) {
+          cp_async4(smem_u32(&dst.lens[t]), sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0 + t);
+          cp_async4(smem_u32(&dst.offs[t]), sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0 + t);
+        } else {
+          dst.lens[t] = 0; dst.offs[t] = 0;
+        }
+      }
+    };
+    for (int c = 0; c < PD; ++c) { prefetch_meta(c); cp_async_commit(); }   // groups 0..PD-1
+    auto publish = [&](int c) {   // the copies of stage c have landed: hand tile and metadata over
+      proxy_fence_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&sm.a_full[c % NBUF]));
+        mbar_arrive(smem_u32(&sm.full_k[c % NSLOT]));
+      }
+    };
+    bool ok = true;
+    int c = 0;
+    for (; c < n_stages; ++c) {
+      const int slot = c % NSLOT, buf = c % NBUF;
+      // metadata slot (c+PD) % MSLOT was last used by stage c - NSLOT
+      if (c >= NSLOT && !mbar_wait(smem_u32(&sm.empty_bar[slot]), (uint32_t)(((c / NSLOT) - 1) & 1), abort_flag)) { ok = false; break; }
+      cp_async_wait<PD - 1>();   // group c (this stage's metadata) is complete
+      const int u = u_begin + c;
+      if (u >= cur_end) { enter_row(cur, u); cur_end = sm.prefix[cur.row + 1]; }
+      StageMeta& mt = sm.meta[0][c % MSLOT];
+      int len = mt.lens[t];
+      const int off = mt.offs[t];
+      if (((len | off) & 7) != 0 || len < 0 || len > R || off < 0 || (int64_t)off + len > sd.flat_stride) {
+        set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
+        len = 0;
+        mt.lens[t] = 0;
+      }
+      // the tensor core must be done with the tile that was in this buffer two stages ago
+      if (c >= NBUF && !mbar_wait(smem_u32(&sm.a_free[buf]), (uint32_t)(((c / NBUF) - 1) & 1), abort_flag)) { ok = false; break; }
+      const unsigned char* row_src = reinterpret_cast<const unsigned char*>(
+          reinterpret_cast<const T*>(sd.flat) + (size_t)cur.arena * sd.flat_stride + (len > 0 ? off : 0));
+      const uint32_t dst = smem_u32(sm.a_tile[buf]) + t * 16;
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const bool in = ch * 8 < len;
+        cp_async16_zfill(dst + ch * 2048, in ? row_src + ch * 16 : row_src, in ? 16 : 0);
+      }
+      prefetch_meta(c + PD);
+      cp_async_commit();                       // group PD + c
+      if (c >= 1) { cp_async_wait<1>(); publish(c - 1); }   // groups up to PD + c - 1 are complete
+    }
+    cp_async_wait<0>();
+    if (ok && n_stages > 0) publish(n_stages - 1);
+  }
+  else if (warp == W_MMA) {
+    // =========================== tensor-core issuer ===========================
+    // K tile = X[128 x 128] . Bk[128 x 128]: eight M=128, N=128, K=16 instructions per stage, fp32
+    // accumulator in tensor-memory buffer c % 2.  Two commits: accumulator ready (consumers) and operand
+    // tile free (gather warps).
+    const uint32_t fmt = (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) ? 1u : 0u;   // 0 = f16, 1 = bf16
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+    const uint32_t basis_addr = smem_u32(sm.basis);
+    for (int c = 0; c < n_stages; ++c) {
+      const int buf = c % NBUF;
+      const uint32_t ph = (uint32_t)((c / NBUF) & 1);
+      if (!mbar_wait(smem_u32(&sm.a_full[buf]), ph, abort_flag)) break;
+      if (c >= NBUF && !mbar_wait(smem_u32(&sm.t_free[buf]), ph ^ 1u, abort_flag)) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t a_addr = smem_u32(sm.a_tile[buf]);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // A: K-major, 8-row core matrices 128 B apart (SBO), the two 8-coefficient chunks 2048 B apart (LBO)
+          // B: MN-major, 8-column core matrices 128 B apart (SBO), the two 8-row groups 2048 B apart (LBO)
+          umma_f16(tmem_base + buf * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
+                   umma_desc(basis_addr + ks * 4096, 2048, 128), idesc, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sm.t_ready[buf]));
+        umma_commit(smem_u32(&sm.a_free[buf]));
+      }
+      __syncwarp();
+    }
+  }
+  else if (warp < NCW) {
   // ============================= consumer warps =============================
-  // 16-token groups are dealt round-robin to the consumer warps: this warp handles groups warp, warp+NCW, ...
-  // of the CTA's stage sequence (group index = stage * 4 + position in stage)
+  // Consumer warp w owns the 16-token group gi = 2*(w&3) + (w>>2) of every stage: those are the tensor-memory
+  // lanes 32*(w&3) + 16*(w>>2) .. +15, the only ones a warp in SM sub-partition w&3 may read.
+  const int gi = 2 * (warp & 3) + (warp >> 2);
+  const uint32_t tmem_lane = (uint32_t)(16 * gi) << 16;
   const int gq = lane >> 2, qq = lane & 3;
   const uint32_t zero_addr = smem_u32(sm.zero_chunk);
-  const uint32_t basis_lane = smem_u32(sm.basis) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * BASIS_PITCH + (lane >> 4) * 16;
   const float4* trig4 = sm.trig;
 
   int row = row0;
-  int grp = warp;             // next group of this warp
+  int c = 0;                  // next stage
   while (row < p.batch && sm.prefix[row] < u_end) {
     const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;   // stages of this row: [.., c_hi)
     float m_run0 = -INFINITY, m_run1 = -INFINITY, l_part0 = 0.f, l_part1 = 0.f;   // heads 2qq, 2qq+1
@@ -542,37 +714,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 #pragma unroll
     for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
 
-    for (; grp < c_hi * GRP_PER_STAGE; grp += NCW) {
-      const int c = grp / GRP_PER_STAGE, gi = grp % GRP_PER_STAGE;
-      const int slot = c % NSLOT;
+    for (; c < c_hi; ++c) {
+      const int slot = c % NSLOT, buf = c % NBUF;
       if (*abort_flag) continue;
       const uint32_t phase = (uint32_t)((c / NSLOT) & 1);
-      if (!mbar_wait(smem_u32(&sm.full_bar[0][slot]), phase, abort_flag)) continue;
-      const StageHdr hdr = sm.hdr[0][slot];
-      int klen = 0;
-      uint32_t koff = 0u;                         // 16-byte chunks from the stage's K base
-      {
-        const StageMeta& mt = sm.meta[0][c % MSLOT];
-        const int tok = gi * 16 + (lane & 15);    // lanes 16..31 mirror lanes 0..15
-        if (tok < hdr.n_tok) {
-          klen = mt.lens[tok];
-          const int ko = mt.offs[tok] - hdr.start;   // elements
-          if (((klen | ko) & 7) != 0 || klen < 0 || klen > R || ko < 0 || ko + klen > hdr.elems) {
-            set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
-            klen = 0;
-          }
-          koff = (uint32_t)ko >> 3;
-        }
-      }
+      if (!mbar_wait(smem_u32(&sm.full_k[slot]), phase, abort_flag)) continue;
+      // lengths as the gather warps left them (0 = token absent or rejected)
+      const int klen = sm.meta[0][c % MSLOT].lens[gi * 16 + (lane & 15)];   // lanes 16..31 mirror lanes 0..15
       const uint32_t valid = __ballot_sync(0xffffffffu, klen > 0) & 0xffffu;
+      // the stage's K tile in tensor memory
+      if (!mbar_wait(smem_u32(&sm.t_ready[buf]), (uint32_t)((c / NBUF) & 1), abort_flag)) continue;
+      tc_fence_after();
+      const uint32_t tmem_tile = tmem_base + tmem_lane + buf * 128;
+      if (valid == 0u) {
+        tc_fence_before();
+        if (lane == 0) mbar_arrive(smem_u32(&sm.t_free[buf]));
+      }
       if (valid != 0u) {
-        const int kmax = __reduce_max_sync(0xffffffffu, klen);
-        // ---------------- K = X . Bk, RoPE, S = K' . Q~^T : two passes over half of the head dims ----------------
-        // Pass h reconstructs dims [32h, 32h+32) and their rotation partners [64+32h, 64+32h+32) (n-tiles
-        // 4h..4h+3 and 8+4h..8+4h+3), rotates them and adds their part of the score, so only 32 accumulator
+        // ---------------- K from tensor memory, RoPE, S = K' . Q~^T : two passes over half of the head dims ----------------
+        // Pass h handles dims [32h, 32h+32) and their rotation partners [64+32h, 64+32h+32): only 32 accumulator
         // registers are live at a time (this is what lets 16 warps fit on the SM).
-        const uint32_t krow = hdr.base + koff * 16u;
-        const int cpar16 = lane >> 4;
         const uint32_t qbase = smem_u32(sm.qrot[slot][gi / (QSUB / 16)]);
         const int qr = lane & 7;   // ldmatrix rows 0..HP-1 = heads, the other rows read the zero chunk
         const uint32_t qaddr = (qr < HP) ? qbase + qr * Q_PITCH + (lane >> 3) * 16 : zero_addr;
@@ -581,37 +742,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         float ss0 = 0.f, ss1 = 0.f;     // sum of squares of the two token rows (K-RMSNorm)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          float acc[8][4];              // [0..3] = n-tiles 4hf+i (dims j), [4..7] = n-tiles 8+4hf+i (dims j+64)
-          uint32_t a[4];
-          ldsm_x4(a, (cpar16 * 8 < klen) ? krow + cpar16 * 16 : zero_addr);
-          // one k-step = 16 latent coefficients: the four basis ldmatrix of the pass are issued ahead of its
-          // eight MMAs and the next step's coefficient fragment is loaded meanwhile; the first step writes
-          // the accumulators (no zero fill), later steps add to them
-          auto kstep = [&](int ks, auto first) {
-            uint32_t an[4] = {0u, 0u, 0u, 0u};
-            if ((ks + 1) * 16 < kmax) {
-              const int chunk = 2 * (ks + 1) + cpar16;
-              ldsm_x4(an, (chunk * 8 < klen) ? krow + chunk * 16 : zero_addr);
-            }
-            const uint32_t brow = basis_lane + ks * 16 * BASIS_PITCH;
-            uint32_t bb[4][4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)   // n-tile pairs: 2hf, 2hf+1 (low dims) and 4+2hf, 4+2hf+1 (partners)
-              ldsm_x4_t_const(bb[j], brow + ((j >> 1) * 4 + 2 * hf + (j & 1)) * 32);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (decltype(first)::value) {
-                Mma<T>::run0(acc[2 * j], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
-                Mma<T>::run0(acc[2 * j + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
-              } else {
-                Mma<T>::run(acc[2 * j], a[0], a[1], a[2], a[3], bb[j][0], bb[j][1]);
-                Mma<T>::run(acc[2 * j + 1], a[0], a[1], a[2], a[3], bb[j][2], bb[j][3]);
-              }
-            }
-            a[0] = an[0]; a[1] = an[1]; a[2] = an[2]; a[3] = an[3];
-          };
-          kstep(0, std::true_type{});
-          for (int ks = 1; ks * 16 < kmax; ++ks) kstep(ks, std::false_type{});
+          // this group's K rows, dims [32hf, 32hf+32) and their rotation partners [64+32hf, ..): acc[0..3] =
+          // n-tiles 4hf+i (dims j), acc[4..7] = n-tiles 8+4hf+i (dims j+64), in the mma.sync accumulator layout
+          float acc[8][4];
+          tmem_ld_2x_16x32(acc, tmem_tile + 32 * hf, tmem_tile + 64 + 32 * hf);
+          if (hf == 1) {   // both halves are in registers: the accumulator buffer may be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm.t_free[buf]));
+          }
           if (KNORM) {
             // RMSNorm of K (Qwen3): the weight is applied here, the per-token 1/rms scales the score at the end
 #pragma unroll
@@ -689,8 +828,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           for (int i = 0; i < 8; ++i) { oacc[i][0] *= al0; oacc[i][1] *= al1; oacc[i][2] *= al0; oacc[i][3] *= al1; }
         }
         // ---------------- O^T[r x heads] += XV^T . P ----------------
-        if (mbar_wait(smem_u32(&sm.full_bar[1][slot]), phase, abort_flag)) {
-          const StageHdr hv = sm.hdr[1][slot];
+        if (mbar_wait(smem_u32(&sm.full_v[slot]), phase, abort_flag)) {
+          const StageHdr hv = sm.hdr[slot];
           const StageMeta& mv = sm.meta[1][c % MSLOT];
           const int tv = gi * 16 + (lane & 7) + 8 * (lane >> 4);   // token whose row this lane addresses
           int vlen_t = 0;
@@ -721,7 +860,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         }
       } else {
         // nothing to do for this group, but its V bytes must have landed before the slot is handed back
-        mbar_wait(smem_u32(&sm.full_bar[1][slot]), phase, abort_flag);
+        mbar_wait(smem_u32(&sm.full_v[slot]), phase, abort_flag);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sm.empty_bar[slot]));
@@ -808,6 +947,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       consumer_bar();
     }
     ++row;
+  }
+  }   // consumer warps
+
+  // ---- epilogue: every warp arrives here; the tensor memory is returned by the warp that allocated it ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == W_MMA) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
   }
   if (*abort_flag && tid == 0) set_status(p.status, DKV_ST_OVERFLOW);
 }
@@ -912,7 +1060,7 @@ __global__ void __launch_bounds__(128) split_combine_kernel(dkv_attn_args p) {
 }
 
 // ------------------------------------------------------------------ host side
-static size_t smem_bytes() { return sizeof(SmemLayout) + 128; }
+static size_t smem_bytes() { return sizeof(SmemLayout) + 1024; }
 
 bool mma_path_ok(const dkv_attn_args* a) {
   if (a->dtype != DKV_F16 && a->dtype != DKV_BF16) return false;

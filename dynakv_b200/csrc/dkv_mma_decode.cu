@@ -738,7 +738,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         const int qr = lane & 7;   // ldmatrix rows 0..HP-1 = heads, the other rows read the zero chunk
         const uint32_t qaddr = (qr < HP) ? qbase + qr * Q_PITCH + (lane >> 3) * 16 : zero_addr;
         const int tA = (gi & (QSUB / 16 - 1)) * 16 + gq, tB = tA + 8;   // offsets inside the 64-token sub-stage
-        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f}, sacc2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains: low dims / partners
         float ss0 = 0.f, ss1 = 0.f;     // sum of squares of the two token rows (K-RMSNorm)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
@@ -795,14 +795,45 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           ldsm_x4(qh, (qr < HP) ? qaddr + (2 + hf) * 64 : zero_addr);
           Mma<T>::run(sacc, kl[0][0], kl[0][1], kl[1][0], kl[1][1], ql[0], ql[1]);
           Mma<T>::run(sacc, kl[2][0], kl[2][1], kl[3][0], kl[3][1], ql[2], ql[3]);
-          Mma<T>::run(sacc, kh[0][0], kh[0][1], kh[1][0], kh[1][1], qh[0], qh[1]);
-          Mma<T>::run(sacc, kh[2][0], kh[2][1], kh[3][0], kh[3][1], qh[2], qh[3]);
+          Mma<T>::run(sacc2, kh[0][0], kh[0][1], kh[1][0], kh[1][1], qh[0], qh[1]);
+          Mma<T>::run(sacc2, kh[2][0], kh[2][1], kh[3][0], kh[3][1], qh[2], qh[3]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sacc[i] += sacc2[i];
         if (KNORM) {
           ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
           ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
           const float rs0 = rsqrtf(ss0 * (1.0f / D) + p.k_norm_eps), rs1 = rsqrtf(ss1 * (1.0f / D) + p.k_norm_eps);
           sacc[0] *= rs0; sacc[1] *= rs0; sacc[2] *= rs1; sacc[3] *= rs1;
+        }
+        // ---------------- V fragments: fetched now, used after the softmax ----------------
+        const bool v_ok = mbar_wait(smem_u32(&sm.full_v[slot]), phase, abort_flag);
+        uint32_t va[8][4];
+        int vmax = 0;
+        if (v_ok) {
+          const StageHdr hv = sm.hdr[slot];
+          const StageMeta& mv = sm.meta[1][c % MSLOT];
+          const int tv = gi * 16 + (lane & 7) + 8 * (lane >> 4);   // token whose row this lane addresses
+          int vlen_t = 0;
+          uint32_t vrow = zero_addr;
+          if (tv < hv.n_tok) {
+            vlen_t = mv.lens[tv];
+            const int vo = mv.offs[tv] - hv.start;
+            if (((vlen_t | vo) & 7) != 0 || vlen_t < 0 || vlen_t > R || vo < 0 || vo + vlen_t > hv.elems) {
+              set_status(p.status, DKV_ST_BAD_LENGTH);
+              vlen_t = 0;
+            }
+            vrow = hv.base + ((uint32_t)vo >> 3) * 16u;
+          }
+          vmax = __reduce_max_sync(0xffffffffu, vlen_t);
+          const int cpar = (lane >> 3) & 1;
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            if (mt * 16 < vmax) {
+              const int chunk = 2 * mt + cpar;
+              ldsm_x4_t(va[mt], (chunk * 8 < vlen_t) ? vrow + chunk * 16 : zero_addr);
+            }
+          }
         }
         // ---------------- online softmax (base 2) ----------------
         // this lane: tokens gq and gq+8, heads 2qq and 2qq+1; head maxima are reduced over the 8 token lanes
@@ -828,35 +859,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           for (int i = 0; i < 8; ++i) { oacc[i][0] *= al0; oacc[i][1] *= al1; oacc[i][2] *= al0; oacc[i][3] *= al1; }
         }
         // ---------------- O^T[r x heads] += XV^T . P ----------------
-        if (mbar_wait(smem_u32(&sm.full_v[slot]), phase, abort_flag)) {
-          const StageHdr hv = sm.hdr[slot];
-          const StageMeta& mv = sm.meta[1][c % MSLOT];
-          const int tv = gi * 16 + (lane & 7) + 8 * (lane >> 4);   // token whose row this lane addresses
-          int vlen_t = 0;
-          uint32_t vrow = zero_addr;
-          if (tv < hv.n_tok) {
-            vlen_t = mv.lens[tv];
-            const int vo = mv.offs[tv] - hv.start;
-            if (((vlen_t | vo) & 7) != 0 || vlen_t < 0 || vlen_t > R || vo < 0 || vo + vlen_t > hv.elems) {
-              set_status(p.status, DKV_ST_BAD_LENGTH);
-              vlen_t = 0;
-            }
-            vrow = hv.base + ((uint32_t)vo >> 3) * 16u;
-          }
-          const int vmax = __reduce_max_sync(0xffffffffu, vlen_t);
-          const int cpar = (lane >> 3) & 1;
-          uint32_t va[8][4];
 #pragma unroll
-          for (int mt = 0; mt < 8; ++mt) {
-            if (mt * 16 < vmax) {
-              const int chunk = 2 * mt + cpar;
-              ldsm_x4_t(va[mt], (chunk * 8 < vlen_t) ? vrow + chunk * 16 : zero_addr);
-            }
-          }
-#pragma unroll
-          for (int mt = 0; mt < 8; ++mt) {
-            if (mt * 16 < vmax) Mma<T>::run(oacc[mt], va[mt][0], va[mt][1], va[mt][2], va[mt][3], pb0, pb1);
-          }
+        for (int mt = 0; mt < 8; ++mt) {
+          if (mt * 16 < vmax) Mma<T>::run(oacc[mt], va[mt][0], va[mt][1], va[mt][2], va[mt][3], pb0, pb1);
         }
       } else {
         // nothing to do for this group, but its V bytes must have landed before the slot is handed back

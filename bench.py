@@ -49,7 +49,7 @@ N_Q_HEADS, N_KV_HEADS, HEAD_DIM = 32, 8, 128
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one split-kernel launch divided by its algorithmic bytes,
 # from the ncu capture summarised under profiles/; None until such a capture exists.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.18   # dram read+write / algorithmic bytes, profile_b2_s32768 capture
 
 
 def measured_peak():

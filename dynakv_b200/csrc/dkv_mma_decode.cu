@@ -4,19 +4,24 @@
 //   * the long-cache split path: a persistent grid that partitions each KV head's token space
 //     evenly over CTAs and writes (m, l, latent accumulator) partials, merged by a combine kernel.
 //
-// Per CTA 16 warps work on 128-token stages:
-//   4 gather warps : copy each token's ragged coefficient row (16-byte cp.async, zero fill past the row's
-//                    length) into a K-major, unswizzled operand tile in shared memory;
-//   1 MMA warp     : K[128 x 128] = X[128 x 128] . Bk with eight tcgen05.mma (M=128, N=128, K=16), the
-//                    accumulator in tensor memory (two 128-column buffers), completion by tcgen05.commit;
-//   1 V loader     : the stage's V bytes are one contiguous range (rows are gap-free): cp.async.bulk into
-//                    a shared-memory ring, mbarrier transaction completion;
-//   1 rotator      : q~ = scale . R(-s0) q per 64-token sub-stage, so consumers rotate K only locally;
-//   8 consumers    : one 16-token group each per stage.  tcgen05.ld.16x256b brings the group's K rows into
-//                    registers in the mma.sync accumulator layout; RoPE in fp32 (pairs (j, j+64) sit in
-//                    one thread); S = K'.q~^T with mma.sync reusing the fragments as A operand; online
-//                    softmax (exp2, shuffles); O^T[r x heads] += XV^T . P with mma.sync, XV read by
-//                    ldmatrix.trans straight from the ragged V bytes.
+// A CTA works on 128-token tiles; all three matrix products of a tile run on the 5th-generation tensor
+// core (tcgen05.mma, accumulators in tensor memory), and each of 128 "token threads" owns one token row
+// of the tile (tensor-memory lane = token), so neither RoPE nor the softmax needs a shuffle:
+//   2+2 gather warps : copy each token's ragged K / V coefficient row (16-byte cp.async, zero fill past the
+//                      row's length) into K-major, unswizzled 128 x 128 operand tiles in shared memory;
+//   2 MMA threads    : per tile  (1) K = X . Bk          M=128 tokens, N=128, K=128 (A, B from shared memory)
+//                                (2) S = K' . Q~^T       M=128 tokens, N=16,  K=128 (A = K' in tensor memory)
+//                                (3) O^T += XV^T . P     M=128 latent, N=16,  K=128 tokens (accumulates per row);
+//                      completion of each product is signalled by tcgen05.commit on mbarriers;
+//   1 rotator warp   : Q~ = scale . R(-s) q for the four 32-token quarters of a tile (the B operand of (2)),
+//                      so token threads rotate K only by their local offset 0..31;
+//   2 x 4 token warps: group g takes tiles of parity g.  A thread reads its token's K row from tensor memory
+//                      (tcgen05.ld.32x32b), applies [RMSNorm and] RoPE in fp32 with its 64 (cos, sin) pairs,
+//                      which also live in tensor memory (they depend on the lane only), and writes K' back as
+//                      packed 16-bit pairs (tcgen05.st) for product (2); then reads its four scores, takes
+//                      p = exp2(s - m_ref) against a per-group reference maximum that is only raised (with a
+//                      rescale of O in tensor memory) when a tile exceeds it by more than 2^8, and stores P
+//                      for product (3).
 //
 // Reference math: src/dynakv/kernels/fused.py:28-142 (fused), two_stage.py:52-157,211-281 (two-stage;
 // the latent-space V accumulation with one up-projection at the end is two_stage.py:261-277).
@@ -29,64 +34,63 @@
 namespace dkv {
 
 constexpr int D = 128;
-constexpr int NCW = 8;                 // consumer warps (warp w owns TMEM lanes 32(w&3)+16(w>>2) .. +15)
+constexpr int NGROUP = 2;              // token-thread groups: warps 0-3 (even tiles), 4-7 (odd tiles)
+constexpr int NCW = 4 * NGROUP;        // token warps
 constexpr int W_ROT = 8;               // query rotator
-constexpr int W_VLOAD = 9;             // V loader
-constexpr int W_GATHER0 = 10;          // gather warps 10..13 (32 tokens of the stage each)
-constexpr int N_GATHER = 4;
-constexpr int W_MMA = 14;              // tcgen05.mma issuer, owns the tensor-memory allocation
-constexpr int NTHREADS = 16 * 32;      // 4 warps per SM sub-partition, 128 registers per thread
-constexpr int ST_TOK = 128;            // tokens per stage = rows of one UMMA
-constexpr int QSUB = 64;               // tokens per query-rotation sub-stage (extent of the local RoPE table)
-constexpr int GRP_PER_STAGE = ST_TOK / 16;  // 16-token groups, one per consumer warp
-constexpr int NSLOT = 4;               // stages in flight (metadata, rotated queries, V bytes)
-constexpr int PD = 4;                  // prefetch distance for the stage metadata (stages)
-constexpr int MSLOT = NSLOT + PD;      // metadata staging slots
-constexpr int NBUF = 2;                // K operand tiles in shared memory = accumulator buffers in tensor memory
-constexpr int A_TILE_BYTES = ST_TOK * 128 * 2;   // 128 tokens x 128 coefficients, chunk-major (see gather)
-constexpr int TMEM_COLS = NBUF * 128;  // fp32 accumulator columns
-constexpr int Q_PITCH = 272;
+constexpr int W_MMA = 9;               // tcgen05.mma issuer, owns the tensor-memory allocation
+constexpr int W_KG0 = 10;              // K gather warps 10, 11 (64 tokens of the tile each)
+constexpr int W_VG0 = 12;              // V gather warps 12, 13
+constexpr int W_PV = 14;               // second tcgen05.mma issuer: product (3)
+constexpr int NTHREADS = 16 * 32;      // warp 15 is idle; 128 registers per thread
+constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
+constexpr int QSUB = 32;               // tokens per query-rotation quarter (= one token warp)
+constexpr int NBUF_A = 2;              // K operand tiles (= K accumulator buffers in tensor memory)
+constexpr int NBUF_V = 3;              // V operand tiles
+constexpr int NQ = 2;                  // rotated-query tiles
+constexpr int PD = 2;                  // prefetch distance of the gather warps' metadata (tiles)
+constexpr int MSLOT = PD + 1;          // metadata staging slots (private to the lane that fetched them)
+constexpr int KV_RING = 8;             // tiles of token-validity masks kept
+constexpr int TILE_BYTES = ST_TOK * 128 * 2;   // 128 tokens x 128 coefficients, chunk-major
+constexpr int Q_LBO = 272;             // byte distance of the 8-dim chunks of the rotated-query tile (bank spread)
+constexpr int Q_TILE_BYTES = 16 * Q_LBO;
 constexpr int HP = 4;                  // query heads per KV head supported by this kernel
-constexpr int RING_BYTES = 36 * 1024;  // V ring; >= one worst-case stage (128 tokens x 256 B)
 constexpr int MAX_BATCH = 1024;
 constexpr int PART_STRIDE = 2 + 128;   // floats per (head) partial record: m, l, latent[128]
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-
-struct __align__(16) StageHdr {   // V side of one stage
-  uint32_t base;    // shared-memory byte address of the stage's bytes
-  int32_t n_tok;
-  int32_t start;    // arena element offset of the stage's first coefficient
-  int32_t elems;    // elements copied for the stage (0 when the stage was rejected)
-};
-
-struct StageMeta {   // raw slices of one side's cache metadata for one stage, copied asynchronously
-  alignas(16) int lens[ST_TOK];
-  alignas(16) int offs[ST_TOK];
-};
+constexpr float M_SLACK = 8.f;         // a tile may exceed the reference maximum by 2^8 before O is rescaled
+// tensor-memory columns (fp32 cells): two K accumulators, the RoPE table, two score tiles, two O accumulators
+constexpr uint32_t TM_K = 0, TM_TRIG = 256, TM_S = 384, TM_O = 416, TMEM_COLS = 512;
 
 struct SmemLayout {
-  alignas(1024) unsigned char a_tile[NBUF][A_TILE_BYTES];   // chunk c (8 coefficients) of token t at c*2048 + t*16
+  alignas(1024) unsigned char a_tile[NBUF_A][TILE_BYTES];   // chunk c (8 coefficients) of token t at c*2048 + t*16
+  alignas(1024) unsigned char v_tile[NBUF_V][TILE_BYTES];   // same layout; [NBUF_V-1] stages the RoPE table in the prologue
   alignas(1024) unsigned char basis[128 * 256];             // Bk[r][d] at (r/8)*2048 + (d/8)*128 + (r%8)*16 + (d%8)*2
-  alignas(128) unsigned char ring[RING_BYTES];
-  alignas(16) float4 trig[QSUB * 64 / 2];            // [t][nt ^ (t&7)][q] -> {c_j, c_j+1, s_j, s_j+1}
-  alignas(16) unsigned char qrot[NSLOT][ST_TOK / QSUB][HP * Q_PITCH];
-  alignas(16) StageMeta meta[2][MSLOT];              // [0] K side, [1] V side
-  alignas(16) StageHdr hdr[NSLOT];
-  alignas(16) float merge[NCW][HP][PART_STRIDE];
+  alignas(128) unsigned char qrot[NQ][Q_TILE_BYTES];        // Q~[n][d] at (d/8)*272 + (n/8)*128 + (n%8)*16 + (d%8)*2
+  alignas(128) unsigned char p_tile[NGROUP][ST_TOK * 16];   // P[t][n < 8] at t*16
+  alignas(16) int meta[2][MSLOT][2][ST_TOK];                // [K|V][slot][lens|offs][token]
+  alignas(16) float merge[NGROUP][HP][PART_STRIDE];
+  alignas(16) float tmax[NGROUP][2][4][4];                  // [group][tile parity][warp][head]
+  alignas(16) float lsum[NGROUP][4][4];                     // [group][warp][head]
   alignas(16) float knorm_w[D];
-  alignas(16) unsigned char zero_chunk[16];
-  alignas(8) unsigned long long full_k[NSLOT];    // K metadata (4 gather warps) + rotated queries (rotator)
-  alignas(8) unsigned long long full_v[NSLOT];    // V bytes (loader arrive + transaction bytes)
-  alignas(8) unsigned long long empty_bar[NSLOT]; // 8 consumer groups done with the stage
-  alignas(8) unsigned long long a_full[NBUF];     // operand tile written (4 gather warps)
-  alignas(8) unsigned long long a_free[NBUF];     // operand tile consumed by the tensor core (commit)
-  alignas(8) unsigned long long t_ready[NBUF];    // accumulator buffer written (commit)
-  alignas(8) unsigned long long t_free[NBUF];     // accumulator buffer read out (8 consumer warps)
+  uint32_t kvalid[KV_RING][4];                              // bit l of word w: token 32w + l of the tile has a K row
+  alignas(8) unsigned long long a_full[NBUF_A];    // K operand tile written (2 gather warps)
+  alignas(8) unsigned long long a_free[NBUF_A];    // product (1) done with it (commit)
+  alignas(8) unsigned long long v_full[NBUF_V];    // V operand tile written (2 gather warps)
+  alignas(8) unsigned long long v_free[NBUF_V];    // product (3) done with it (commit)
+  alignas(8) unsigned long long q_full[NQ];        // rotated queries written (rotator)
+  alignas(8) unsigned long long q_free[NQ];        // product (2) done with them (commit)
+  alignas(8) unsigned long long t_ready[NGROUP];   // K accumulator written (commit)
+  alignas(8) unsigned long long kp_ready[NGROUP];  // K' written back to tensor memory (4 token warps)
+  alignas(8) unsigned long long s_ready[NGROUP];   // scores written (commit)
+  alignas(8) unsigned long long p_ready[NGROUP];   // P tile written (4 token warps)
+  alignas(8) unsigned long long pv_done[NGROUP];   // product (3) done: O updated, P tile free (commit)
+  alignas(8) unsigned long long grp_sync[NGROUP];  // per-tile rendezvous of a group's 4 warps (tile maxima)
   int prefix[MAX_BATCH + 1];
-  int ring_start[NSLOT];
   int abort_flag;
   uint32_t tmem_base;
 };
+static_assert(sizeof(SmemLayout) + 1024 <= 227 * 1024, "shared memory budget");
+static_assert(32 * 129 * 4 <= TILE_BYTES, "RoPE staging table must fit in one tile");
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -125,6 +129,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   ok = __shfl_sync(0xffffffffu, ok, 0);
   return ok != 0;
 }
+// The same for a single thread (the tensor-core issuers run on one lane).
+__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+    if (mbar_test(bar, parity)) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
@@ -158,102 +171,88 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// Two 16-row x 32-column fp32 blocks of tensor memory in the mma.sync accumulator layout:
-// v[i][0..3] = n-tile i {(row g, col 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)}, g = lane/4, q = lane%4;
-// v[0..3] from addr_lo, v[4..7] from addr_hi.  The wait is part of the same statement, so no register of
-// the result can be touched before the loads have landed.
-__device__ __forceinline__ void tmem_ld_2x_16x32(float (&v)[8][4], uint32_t addr_lo, uint32_t addr_hi) {
+// tcgen05.mma with the A operand in tensor memory (16-bit pairs packed in 32-bit cells, lane = row)
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Thread-per-lane tensor-memory access (32x32b shapes): thread i of the warp addresses lane (base lane + i),
+// register k holds column (base column + k).  Every load carries its wait in the same statement, so no
+// result register can be touched before the data has landed.
+// One RoPE chunk: 8 K values of dims j0..j0+7, their rotation partners (dims +64) and the 16 table cells.
+__device__ __forceinline__ void tmem_ld_rope_chunk(float (&lo)[8], float (&hi)[8], float (&tg)[16], uint32_t a_lo,
+                                                   uint32_t a_hi, uint32_t a_tg) {
   uint32_t r[32];
   asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%32];\n"
-      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%33];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%32];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%8,%9,%10,%11,%12,%13,%14,%15}, [%33];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%34];\n"
       "tcgen05.wait::ld.sync.aligned;"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(addr_lo), "r"(addr_hi)
+      : "r"(a_lo), "r"(a_hi), "r"(a_tg)
       : "memory");
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < 8; ++i) { lo[i] = __uint_as_float(r[i]); hi[i] = __uint_as_float(r[8 + i]); }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[i][j] = __uint_as_float(r[4 * i + j]);
+  for (int i = 0; i < 16; ++i) tg[i] = __uint_as_float(r[16 + i]);
+}
+__device__ __forceinline__ void tmem_ld4(float (&v)[4], uint32_t addr) {
+  uint32_t r[4];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];\ntcgen05.wait::ld.sync.aligned;"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const float (&v)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+                 "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+                 "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+                 "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+                 "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+               : "memory");
 }
 
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
 
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
+// order-preserving map float -> int (and back: the map is its own inverse), for redux.sync
+__device__ __forceinline__ int float_key(float f) {
+  const int i = __float_as_int(f);
+  return i ^ ((i >> 31) & 0x7fffffff);
 }
-__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-
-// Loads of data that does not change after the prologue barrier (the basis) carry no ordering
-// constraint, so the compiler is free to hoist and batch them.
-__device__ __forceinline__ void ldsm_x4_t_const(uint32_t (&r)[4], uint32_t addr) {
-  asm("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-      : "r"(addr));
-}
-
-// 8x8 transpose of 16-bit elements across the warp: lane (g, q) gives row g, columns 2q,2q+1 and
-// receives row g, columns 2q,2q+1 of the transposed matrix.
-__device__ __forceinline__ uint32_t movmatrix_t(uint32_t x) {
-  uint32_t y;
-  asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
+__device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
+__device__ __forceinline__ float warp_max_redux(float v) { return key_float(__reduce_max_sync(0xffffffffu, float_key(v))); }
 
 template <typename T>
-struct Mma;
+struct Pack;
 template <>
-struct Mma<__nv_bfloat16> {
-  static __device__ __forceinline__ void run(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                             uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  }
-  static __device__ __forceinline__ void run0(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {   // c = a.b (no accumulator input)
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-  }
-  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+struct Pack<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t two(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   }
 };
 template <>
-struct Mma<__half> {
-  static __device__ __forceinline__ void run(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                             uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  }
-  static __device__ __forceinline__ void run0(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-  }
-  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+struct Pack<__half> {
+  static __device__ __forceinline__ uint32_t two(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   }
 };
 
 // --------------------------------------------------------------- work partition
-// Token space of one KV head: batch rows back to back, each rounded up to whole 64-token units.
+// Token space of one KV head: batch rows back to back, each rounded up to whole 128-token tiles.
 __device__ __forceinline__ int row_tokens(const dkv_attn_args& p, int i) {
   const int b = p.batch_index ? p.batch_index[i] : i;
   int s = p.seq_len;
@@ -271,9 +270,12 @@ struct WsHeader {  // start of the split workspace, written by the split kernel,
 };
 __host__ __device__ constexpr size_t ws_header_bytes() { return (sizeof(WsHeader) + 255) / 256 * 256; }
 
+// per-row facts cached by the warps that walk the tile sequence
+struct RowInfo { int row, arena, tokens, first_unit; };
+
 // ------------------------------------------------------------------ the kernel
 template <typename T, bool FUSED, bool KNORM>
-__global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p, float log_theta, int n_cta, int meta16) {
+__global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p, float log_theta, int n_cta) {
   extern __shared__ unsigned char smem_raw[];
   SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
@@ -285,7 +287,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 
   // ---- prologue A: partition table and barriers --------------------------------------------------
   if (warp == 0) {
-    // inclusive scan of the per-row unit counts, 32 rows at a time
+    // inclusive scan of the per-row tile counts, 32 rows at a time
     int carry = 0;
     for (int base = 0; base < p.batch; base += 32) {
       const int i = base + lane;
@@ -301,21 +303,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     if (lane == 0) {
       sm.prefix[0] = 0;
       sm.abort_flag = 0;
-      for (int s = 0; s < NSLOT; ++s) {
-        mbar_init(smem_u32(&sm.full_k[s]), N_GATHER + 1);      // gather warps (metadata) + rotator
-        mbar_init(smem_u32(&sm.full_v[s]), 1);                 // V loader (with tx bytes)
-        mbar_init(smem_u32(&sm.empty_bar[s]), GRP_PER_STAGE);  // one arrival per 16-token group
-      }
-      for (int s = 0; s < NBUF; ++s) {
-        mbar_init(smem_u32(&sm.a_full[s]), N_GATHER);
-        mbar_init(smem_u32(&sm.a_free[s]), 1);
+      for (int s = 0; s < NBUF_A; ++s) { mbar_init(smem_u32(&sm.a_full[s]), 2); mbar_init(smem_u32(&sm.a_free[s]), 1); }
+      for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 2); mbar_init(smem_u32(&sm.v_free[s]), 1); }
+      for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 1); mbar_init(smem_u32(&sm.q_free[s]), 1); }
+      for (int s = 0; s < NGROUP; ++s) {
         mbar_init(smem_u32(&sm.t_ready[s]), 1);
-        mbar_init(smem_u32(&sm.t_free[s]), NCW);
+        mbar_init(smem_u32(&sm.kp_ready[s]), 4);
+        mbar_init(smem_u32(&sm.s_ready[s]), 1);
+        mbar_init(smem_u32(&sm.p_ready[s]), 4);
+        mbar_init(smem_u32(&sm.pv_done[s]), 1);
+        mbar_init(smem_u32(&sm.grp_sync[s]), 4);
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
   }
-  if (tid < 4) reinterpret_cast<uint32_t*>(sm.zero_chunk)[tid] = 0u;
   __syncthreads();
 
   const int total_units = sm.prefix[p.batch];
@@ -346,7 +347,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   }
   if (n_stages <= 0) return;
 
-  // ---- prologue B: basis and local-rotation table (only CTAs that have work) ---------------------
+  // ---- prologue B: basis, tensor memory, RoPE table (only CTAs that have work) --------------------
   {
     // basis rows [R][128] -> the MN-major unswizzled operand layout of the tensor core: 8x8 core matrices,
     // element (r, d) at (r/8)*2048 + (d/8)*128 + (r%8)*16 + (d%8)*2; rows >= R are zero
@@ -357,25 +358,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       if (r < R) v = src[r * 16 + c];
       *reinterpret_cast<uint4*>(sm.basis + (r >> 3) * 2048 + c * 128 + (r & 7) * 16) = v;
     }
-    if (warp == W_MMA) {   // tensor-memory columns for the two accumulator buffers
+    if (warp == W_MMA) {
       asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
                    "r"(TMEM_COLS));
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
-    // local rotation table for offsets t = 0..63: angle = t * f_j, f_j = exp(-(2j/D) ln theta).
-    // NTHREADS is a multiple of 64, so a thread keeps one j and steps t by NTHREADS/64: one exact
-    // sincos for its first t, then a fixed-angle rotation per step (error ~1e-7 per step, <= 11 steps).
+    // RoPE table for local offsets t = 0..31: angle = t * f_j, f_j = exp(-(2j/D) ln theta), staged as
+    // tr[t][4*(j/2) + (j&1)] = cos, [.. + 2] = sin (row pitch 129 floats).  NTHREADS is a multiple of 64, so a
+    // thread keeps one j and steps t by NTHREADS/64: one exact sincos, then a fixed-angle rotation per step.
     static_assert(NTHREADS % 64 == 0, "trig table fill assumes a fixed j per thread");
     constexpr int TSTEP = NTHREADS / 64;
-    float* tr = reinterpret_cast<float*>(sm.trig);
+    float* tr = reinterpret_cast<float*>(sm.v_tile[NBUF_V - 1]);
     const int j = tid & 63;
     const float f = expf(-((float)(2 * j) / (float)D) * log_theta);
     float sn, cs, ds, dc;
     sincosf((float)(tid >> 6) * f, &sn, &cs);
     sincosf((float)TSTEP * f, &ds, &dc);
-    const int nt = j >> 3, q = (j & 7) >> 1;
     for (int t = tid >> 6; t < QSUB; t += TSTEP) {
-      const int idx = ((t * 8 + (nt ^ (t & 7))) * 4 + q) * 4 + (j & 1);
+      const int idx = t * 129 + 4 * (j >> 1) + (j & 1);
       tr[idx] = cs;
       tr[idx + 2] = sn;
       const float c2 = cs * dc - sn * ds, s2 = sn * dc + cs * ds;
@@ -383,11 +383,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
     if (KNORM && tid < D) sm.knorm_w[tid] = p.k_norm_weight[tid];
   }
-  proxy_fence_async();     // the basis was written with ordinary stores and is read by the tensor core
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
+  if (warp < 4) {
+    // the table row of this thread's local offset goes to its tensor-memory lane (both groups read it there)
+    const float* tr = reinterpret_cast<const float*>(sm.v_tile[NBUF_V - 1]) + lane * 129;
+    const uint32_t dst = tmem_base + ((uint32_t)(32 * warp) << 16) + TM_TRIG;
+#pragma unroll
+    for (int blk = 0; blk < 8; ++blk) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = tr[16 * blk + i];
+      tmem_st16(dst + 16 * blk, v);
+    }
+    tmem_wait_st();
+  }
+  proxy_fence_async();     // the basis was written with ordinary stores and is read by the tensor core
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   // first batch row touched by this CTA
   int row0 = 0;
@@ -399,497 +415,398 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
     row0 = FUSED ? (int)blockIdx.x : lo;
   }
+  auto enter_row = [&](RowInfo& ri, int u) {
+    while (u >= sm.prefix[ri.row + 1]) ++ri.row;
+    const int b = p.batch_index ? p.batch_index[ri.row] : ri.row;
+    ri.arena = b * p.arenas_per_batch + g;
+    ri.tokens = row_tokens(p, ri.row);
+    ri.first_unit = sm.prefix[ri.row];
+  };
 
   if (warp == W_ROT) {
     // =========================== query rotator warp ===========================
-    // For every 64-token sub-stage with base position s0 it publishes q~ = scale * R(-s0) q for the
-    // group's heads, so that q~ . R(t) k = q . R(s0 + t) k with the local offset t = 0..63.
-    const float f_lo = expf(-((float)(2 * lane) / (float)D) * log_theta);
-    const float f_hi = expf(-((float)(2 * (lane + 32)) / (float)D) * log_theta);
-    float cda, sda, cdb, sdb;
-    sincosf((float)QSUB * f_lo, &sda, &cda);
-    sincosf((float)QSUB * f_hi, &sdb, &cdb);
+    // For the four 32-token quarters of every tile (base position s) it publishes Q~ = scale * R(-s) q for the
+    // group's heads as row n = 4*quarter + head of the B operand of product (2), so that
+    // q~ . R(t) k = q . R(s + t) k with the local offset t = 0..31.  Lane l owns the pairs j = 2l, 2l+1.
+    const float f0 = expf(-((float)(4 * lane) / (float)D) * log_theta);
+    const float f1 = expf(-((float)(4 * lane + 2) / (float)D) * log_theta);
+    float cd0, sd0, cd1, sd1;
+    sincosf((float)QSUB * f0, &sd0, &cd0);
+    sincosf((float)QSUB * f1, &sd1, &cd1);
     const float qscale = rsqrtf((float)D) * 1.4426950408889634f;  // softmax scale and log2(e) folded into q
-    float qa0[HP], qa1[HP], qb0[HP], qb1[HP];                      // dims lane, lane+64 | lane+32, lane+96
+    float a0[HP], b0[HP], a1[HP], b1[HP];   // (q~_j, q~_{j+64}) for j = 2l and j = 2l+1
     int row = row0;
     for (int c = 0; c < n_stages; ++c) {
-      const int slot = c % NSLOT;
-      if (c >= NSLOT &&
-          !mbar_wait(smem_u32(&sm.empty_bar[slot]), (uint32_t)(((c / NSLOT) - 1) & 1), abort_flag))
-        break;
+      const int slot = c % NQ;
+      if (c >= NQ && !mbar_wait(smem_u32(&sm.q_free[slot]), (uint32_t)(((c / NQ) - 1) & 1), abort_flag)) break;
       const int u = u_begin + c;
       while (u >= sm.prefix[row + 1]) ++row;
       const bool row_start = (c == 0) || (u == sm.prefix[row]);
       const int b = p.batch_index ? p.batch_index[row] : row;
       const int s0 = (u - sm.prefix[row]) * ST_TOK;
+      unsigned char* const qt_base = sm.qrot[slot] + (lane >> 2) * Q_LBO + (lane & 3) * 4;
 #pragma unroll
-      for (int sub = 0; sub < ST_TOK / QSUB; ++sub) {
-        if (row_start && sub == 0) {
+      for (int qt = 0; qt < ST_TOK / QSUB; ++qt) {
+        if (row_start && qt == 0) {
           float sa, ca, sb, cb;
-          sincosf((float)s0 * f_lo, &sa, &ca);
-          sincosf((float)s0 * f_hi, &sb, &cb);
+          sincosf((float)s0 * f0, &sa, &ca);
+          sincosf((float)s0 * f1, &sb, &cb);
 #pragma unroll
           for (int h = 0; h < HP; ++h) {
             float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
             if (h < G) {
               const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)(g * G + h) * p.q_stride_h;
-              x0 = to_f32(qp[lane]) * qscale; x1 = to_f32(qp[lane + 64]) * qscale;
-              y0 = to_f32(qp[lane + 32]) * qscale; y1 = to_f32(qp[lane + 96]) * qscale;
+              x0 = to_f32(qp[2 * lane]) * qscale; x1 = to_f32(qp[2 * lane + 64]) * qscale;
+              y0 = to_f32(qp[2 * lane + 1]) * qscale; y1 = to_f32(qp[2 * lane + 65]) * qscale;
             }
-            qa0[h] = x0 * ca + x1 * sa; qa1[h] = x1 * ca - x0 * sa;
-            qb0[h] = y0 * cb + y1 * sb; qb1[h] = y1 * cb - y0 * sb;
+            a0[h] = x0 * ca + x1 * sa; b0[h] = x1 * ca - x0 * sa;
+            a1[h] = y0 * cb + y1 * sb; b1[h] = y1 * cb - y0 * sb;
           }
         } else {
 #pragma unroll
           for (int h = 0; h < HP; ++h) {
-            const float x0 = qa0[h], x1 = qa1[h], y0 = qb0[h], y1 = qb1[h];
-            qa0[h] = x0 * cda + x1 * sda; qa1[h] = x1 * cda - x0 * sda;
-            qb0[h] = y0 * cdb + y1 * sdb; qb1[h] = y1 * cdb - y0 * sdb;
+            const float x0 = a0[h], x1 = b0[h], y0 = a1[h], y1 = b1[h];
+            a0[h] = x0 * cd0 + x1 * sd0; b0[h] = x1 * cd0 - x0 * sd0;
+            a1[h] = y0 * cd1 + y1 * sd1; b1[h] = y1 * cd1 - y0 * sd1;
           }
         }
 #pragma unroll
         for (int h = 0; h < HP; ++h) {
-          T* qd = reinterpret_cast<T*>(sm.qrot[slot][sub] + h * Q_PITCH);
-          qd[lane] = from_f32<T>(qa0[h]); qd[lane + 64] = from_f32<T>(qa1[h]);
-          qd[lane + 32] = from_f32<T>(qb0[h]); qd[lane + 96] = from_f32<T>(qb1[h]);
+          const int n = qt * HP + h;
+          unsigned char* w = qt_base + (n >> 3) * 128 + (n & 7) * 16;
+          *reinterpret_cast<uint32_t*>(w) = Pack<T>::two(a0[h], a1[h]);                 // dims 2l, 2l+1
+          *reinterpret_cast<uint32_t*>(w + 8 * Q_LBO) = Pack<T>::two(b0[h], b1[h]);     // dims 2l+64, 2l+65
         }
       }
+      proxy_fence_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.full_k[slot]));
+      if (lane == 0) mbar_arrive(smem_u32(&sm.q_full[slot]));
     }
   }
 
-  else if (warp == W_VLOAD) {
-    // =========================== V loader warp ===========================
-    // Per stage: copy the V side's raw lens/offs slices into a staging slot (cp.async, PD stages ahead), read
-    // the stage's first and one-past-last arena offsets from them (rows are gap-free, so the stage is one
-    // contiguous byte range), take ring space, and issue the bulk copy in two halves from two lanes.
-    const dkv_side& sd = p.v;
-    unsigned char* const ring = sm.ring;
-    // per-row facts are cached and refreshed only when the stage sequence enters another batch row
-    struct RowInfo { int row, arena, tokens, first_unit; };
-    auto enter_row = [&](RowInfo& ri, int u) {
-      while (u >= sm.prefix[ri.row + 1]) ++ri.row;
-      const int b = p.batch_index ? p.batch_index[ri.row] : ri.row;
-      ri.arena = b * p.arenas_per_batch + g;
-      ri.tokens = row_tokens(p, ri.row);
-      ri.first_unit = sm.prefix[ri.row];
-    };
-    RowInfo pre{row0, 0, 0, 0}, cur{row0, 0, 0, 0};
-    int pre_end = -1, cur_end = -1;   // first unit past the cached row
-    auto prefetch = [&](int c) {
-      if (c < n_stages) {
-        const int u = u_begin + c;
-        if (u >= pre_end) { enter_row(pre, u); pre_end = sm.prefix[pre.row + 1]; }
-        const int s0 = (u - pre.first_unit) * ST_TOK;
-        StageMeta& dst = sm.meta[1][c % MSLOT];
-        const int32_t* ls = sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0;
-        const int32_t* os = sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0;
-        const int left = pre.tokens - s0;                 // tokens of the row from s0 on (> 0)
-        if (meta16) {
-          // 16-byte copies with zero fill past the row's last token (never reads beyond it)
-          const int t = lane * 4;
-          const int nbytes = min(max(left - t, 0), 4) * 4;
-          cp_async16_zfill(smem_u32(&dst.lens[t]), nbytes ? (const void*)(ls + t) : (const void*)ls, nbytes);
-          cp_async16_zfill(smem_u32(&dst.offs[t]), nbytes ? (const void*)(os + t) : (const void*)os, nbytes);
-        } else {
-#pragma unroll
-          for (int hh = 0; hh < ST_TOK / 32; ++hh) {
-            const int t = lane + 32 * hh;
-            if (t < left) {
-              cp_async4(smem_u32(&dst.lens[t]), ls + t);
-              cp_async4(smem_u32(&dst.offs[t]), os + t);
-            } else {
-              dst.lens[t] = 0; dst.offs[t] = 0;
-            }
-          }
-        }
-      }
-      cp_async_commit();
-    };
-    for (int c = 0; c < PD; ++c) prefetch(c);
-
-    int head = 0;         // ring allocation cursor (state is kept identical on all lanes)
-    int oldest = 0;       // oldest stage whose ring bytes are still owned by consumers
-    bool wrapped = false;
-    bool ok = true;
-    auto release_oldest = [&](int c) -> bool {
-      const bool done = mbar_wait(smem_u32(&sm.empty_bar[oldest % NSLOT]), (uint32_t)((oldest / NSLOT) & 1), abort_flag);
-      if (!done) return false;
-      const int old_start = sm.ring_start[oldest % NSLOT];
-      ++oldest;
-      if (oldest < c) {
-        const int new_start = sm.ring_start[oldest % NSLOT];
-        if (new_start < old_start) wrapped = false;
-      } else {
-        head = 0;
-        wrapped = false;
-      }
-      return true;
-    };
-    for (int c = 0; c < n_stages && ok; ++c) {
-      const int slot = c % NSLOT;
-      // the stage that last used this slot (and the staging slot the next prefetch overwrites) must be done
-      while (ok && oldest <= c - NSLOT) ok = release_oldest(c);
-      if (!ok) break;
-      prefetch(c + PD);
-      cp_async_wait<PD>();
-      __syncwarp();
-      const int u = u_begin + c;
-      if (u >= cur_end) { enter_row(cur, u); cur_end = sm.prefix[cur.row + 1]; }
-      const int s0 = (u - cur.first_unit) * ST_TOK;
-      const int n_tok = min(ST_TOK, cur.tokens - s0);
-      const StageMeta& mt = sm.meta[1][c % MSLOT];
-      const int start_el = mt.offs[0];
-      const int end_el = mt.offs[n_tok - 1] + mt.lens[n_tok - 1];
-      int tot = end_el - start_el;
-      // the byte range must be 16-byte aligned, inside the arena row and no larger than a full stage
-      const bool bad = ((start_el | end_el) & 7) != 0 || start_el < 0 || tot < 0 || tot > ST_TOK * 128 ||
-                       (int64_t)end_el > sd.flat_stride;
-      if (bad) {
-        if (lane == 0) set_status(p.status, DKV_ST_BAD_LENGTH);
-        tot = 0;     // consumers see an empty stage and skip its tokens
-      }
-      const int need = tot * 2;
-
-      int start = 0;
-      while (ok) {
-        if (oldest == c) { start = 0; head = 0; wrapped = false; break; }
-        const int tail = sm.ring_start[oldest % NSLOT];
-        if (!wrapped) {
-          if (head + need <= RING_BYTES) { start = head; break; }
-          if (need <= tail) { start = 0; wrapped = true; break; }
-        } else {
-          if (head + need <= tail) { start = head; break; }
-        }
-        ok = release_oldest(c);
-      }
-      if (!ok) break;
-      head = start + need;
-      __syncwarp();
-      const uint32_t bar = smem_u32(&sm.full_v[slot]);
-      const uint32_t base = smem_u32(ring + start);
-      if (lane == 2) {
-        sm.ring_start[slot] = start;
-        StageHdr h;
-        h.base = base; h.n_tok = n_tok; h.start = start_el; h.elems = tot;
-        sm.hdr[slot] = h;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)need);
-      // a thread sustains only a few bulk copies per microsecond: the range is cut in two 16-byte aligned
-      // halves issued by two lanes; both complete on the same barrier
-      if (lane < 2) {
-        const int first = (need / 2) & ~15;
-        const int off = lane ? first : 0, len = lane ? need - first : first;
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(
-            reinterpret_cast<const T*>(sd.flat) + (size_t)cur.arena * sd.flat_stride + start_el);
-        if (len > 0) bulk_g2s(base + (uint32_t)off, src + off, (uint32_t)len, bar);
-      }
-    }
-    cp_async_wait<0>();
-    if (!ok && lane == 0) set_status(p.status, DKV_ST_OVERFLOW);
-  }
-
-  else if (warp >= W_GATHER0 && warp < W_GATHER0 + N_GATHER) {
+  else if (warp >= W_KG0 && warp < W_KG0 + 4) {
     // =========================== gather warps ===========================
-    // Lane l of gather warp j owns token 32j + l of every stage: it stages the token's length and offset
-    // (cp.async, PD stages ahead) and copies the token's coefficient row into the operand tile, one 16-byte
-    // chunk per cp.async, chunk c of token t at c*2048 + t*16; chunks past the row's length are zero-filled
-    // (source size 0), so the tensor core always multiplies a full 128 x 128 tile.
-    const int t = (warp - W_GATHER0) * 32 + lane;
-    const dkv_side& sd = p.k;
-    struct RowInfo { int row, arena, tokens, first_unit; };
-    auto enter_row = [&](RowInfo& ri, int u) {
-      while (u >= sm.prefix[ri.row + 1]) ++ri.row;
-      const int b = p.batch_index ? p.batch_index[ri.row] : ri.row;
-      ri.arena = b * p.arenas_per_batch + g;
-      ri.tokens = row_tokens(p, ri.row);
-      ri.first_unit = sm.prefix[ri.row];
-    };
+    // Lane l of gather warp j (of its side) owns tokens 64j + l and 64j + 32 + l of every tile: it stages their
+    // lengths and offsets (cp.async, PD tiles ahead, slots private to the lane) and copies each coefficient row
+    // into the operand tile, one 16-byte chunk per cp.async, chunk c of token t at c*2048 + t*16; chunks past
+    // the row's length are zero-filled (source size 0), so the tensor core always sees a full 128 x 128 tile.
+    const bool is_v = warp >= W_VG0;
+    const int gw = (warp - W_KG0) & 1;
+    const dkv_side& sd = is_v ? p.v : p.k;
+    const int side = is_v ? 1 : 0;
+    const int NB = is_v ? NBUF_V : NBUF_A;
+    const int tA = 64 * gw + lane;
     RowInfo pre{row0, 0, 0, 0}, cur{row0, 0, 0, 0};
     int pre_end = -1, cur_end = -1;
-    auto prefetch_meta = [&](int c) {   // no commit: the caller groups it with the stage's data copies
+    auto prefetch_meta = [&](int c) {   // no commit: the caller groups it with the tile's data copies
       if (c < n_stages) {
         const int u = u_begin + c;
         if (u >= pre_end) { enter_row(pre, u); pre_end = sm.prefix[pre.row + 1]; }
         const int s0 = (u - pre.first_unit) * ST_TOK;
-        StageMeta& dst = sm.meta[0][c % MSLOT];
-        if (s0 + t < pre.tokens) {
-          cp_async4(smem_u32(&dst.lens[t]), sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0 + t);
-          cp_async4(smem_u32(&dst.offs[t]), sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0 + t);
-        } else {
-          dst.lens[t] = 0; dst.offs[t] = 0;
+        int(*dst)[ST_TOK] = sm.meta[side][c % MSLOT];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int t = tA + 32 * k;
+          if (s0 + t < pre.tokens) {
+            cp_async4(smem_u32(&dst[0][t]), sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0 + t);
+            cp_async4(smem_u32(&dst[1][t]), sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0 + t);
+          } else {
+            dst[0][t] = 0; dst[1][t] = 0;
+          }
         }
       }
     };
     for (int c = 0; c < PD; ++c) { prefetch_meta(c); cp_async_commit(); }   // groups 0..PD-1
-    auto publish = [&](int c) {   // the copies of stage c have landed: hand tile and metadata over
+    auto publish = [&](int c) {   // the copies of tile c have landed: hand the tile over
       proxy_fence_async();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(smem_u32(&sm.a_full[c % NBUF]));
-        mbar_arrive(smem_u32(&sm.full_k[c % NSLOT]));
-      }
+      if (lane == 0) mbar_arrive(smem_u32(is_v ? &sm.v_full[c % NBUF_V] : &sm.a_full[c % NBUF_A]));
     };
     bool ok = true;
-    int c = 0;
-    for (; c < n_stages; ++c) {
-      const int slot = c % NSLOT, buf = c % NBUF;
-      // metadata slot (c+PD) % MSLOT was last used by stage c - NSLOT
-      if (c >= NSLOT && !mbar_wait(smem_u32(&sm.empty_bar[slot]), (uint32_t)(((c / NSLOT) - 1) & 1), abort_flag)) { ok = false; break; }
-      cp_async_wait<PD - 1>();   // group c (this stage's metadata) is complete
+    for (int c = 0; c < n_stages; ++c) {
+      const int buf = c % NB;
+      cp_async_wait<PD - 1>();   // group c (this tile's metadata) is complete
       const int u = u_begin + c;
       if (u >= cur_end) { enter_row(cur, u); cur_end = sm.prefix[cur.row + 1]; }
-      StageMeta& mt = sm.meta[0][c % MSLOT];
-      int len = mt.lens[t];
-      const int off = mt.offs[t];
-      if (((len | off) & 7) != 0 || len < 0 || len > R || off < 0 || (int64_t)off + len > sd.flat_stride) {
-        set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
-        len = 0;
-        mt.lens[t] = 0;
-      }
-      // the tensor core must be done with the tile that was in this buffer two stages ago
-      if (c >= NBUF && !mbar_wait(smem_u32(&sm.a_free[buf]), (uint32_t)(((c / NBUF) - 1) & 1), abort_flag)) { ok = false; break; }
-      const unsigned char* row_src = reinterpret_cast<const unsigned char*>(
-          reinterpret_cast<const T*>(sd.flat) + (size_t)cur.arena * sd.flat_stride + (len > 0 ? off : 0));
-      const uint32_t dst = smem_u32(sm.a_tile[buf]) + t * 16;
+      int(*mt)[ST_TOK] = sm.meta[side][c % MSLOT];
+      int len[2], off[2];
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const bool in = ch * 8 < len;
-        cp_async16_zfill(dst + ch * 2048, in ? row_src + ch * 16 : row_src, in ? 16 : 0);
+      for (int k = 0; k < 2; ++k) {
+        len[k] = mt[0][tA + 32 * k];
+        off[k] = mt[1][tA + 32 * k];
+        if (((len[k] | off[k]) & 7) != 0 || len[k] < 0 || len[k] > R || off[k] < 0 || (int64_t)off[k] + len[k] > sd.flat_stride) {
+          set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
+          len[k] = 0;
+        }
+      }
+      if (!is_v) {
+        const uint32_t m0 = __ballot_sync(0xffffffffu, len[0] > 0), m1 = __ballot_sync(0xffffffffu, len[1] > 0);
+        if (lane == 0) { sm.kvalid[c % KV_RING][2 * gw] = m0; sm.kvalid[c % KV_RING][2 * gw + 1] = m1; }
+      }
+      // the tensor core must be done with the tile that was in this buffer NB tiles ago
+      if (c >= NB && !mbar_wait(smem_u32(is_v ? &sm.v_free[buf] : &sm.a_free[buf]), (uint32_t)(((c / NB) - 1) & 1), abort_flag)) {
+        ok = false;
+        break;
+      }
+      unsigned char* const tile = is_v ? sm.v_tile[buf] : sm.a_tile[buf];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const unsigned char* row_src = reinterpret_cast<const unsigned char*>(
+            reinterpret_cast<const T*>(sd.flat) + (size_t)cur.arena * sd.flat_stride + (len[k] > 0 ? off[k] : 0));
+        const uint32_t dst = smem_u32(tile) + (tA + 32 * k) * 16;
+#pragma unroll
+        for (int ch = 0; ch < 16; ++ch) {
+          const bool in = ch * 8 < len[k];
+          cp_async16_zfill(dst + ch * 2048, in ? row_src + ch * 16 : row_src, in ? 16 : 0);
+        }
       }
       prefetch_meta(c + PD);
       cp_async_commit();                       // group PD + c
       if (c >= 1) { cp_async_wait<1>(); publish(c - 1); }   // groups up to PD + c - 1 are complete
     }
     cp_async_wait<0>();
-    if (ok && n_stages > 0) publish(n_stages - 1);
+    if (ok) publish(n_stages - 1);
   }
+
   else if (warp == W_MMA) {
-    // =========================== tensor-core issuer ===========================
-    // K tile = X[128 x 128] . Bk[128 x 128]: eight M=128, N=128, K=16 instructions per stage, fp32
-    // accumulator in tensor-memory buffer c % 2.  Two commits: accumulator ready (consumers) and operand
-    // tile free (gather warps).
-    const uint32_t fmt = (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) ? 1u : 0u;   // 0 = f16, 1 = bf16
-    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-    const uint32_t basis_addr = smem_u32(sm.basis);
-    for (int c = 0; c < n_stages; ++c) {
-      const int buf = c % NBUF;
-      const uint32_t ph = (uint32_t)((c / NBUF) & 1);
-      if (!mbar_wait(smem_u32(&sm.a_full[buf]), ph, abort_flag)) break;
-      if (c >= NBUF && !mbar_wait(smem_u32(&sm.t_free[buf]), ph ^ 1u, abort_flag)) break;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t a_addr = smem_u32(sm.a_tile[buf]);
+    // =========================== tensor-core issuer 1: products (1) and (2) ===========================
+    // One lane runs the whole loop.  Step i issues product (1) of tile i, then product (2) of tile i-1, each
+    // after the barriers that say its operands are in place.  The tensor core executes one thread's
+    // instructions in issue order, which also orders the re-use of the accumulator buffers: tile i+2 overwrites
+    // K' of tile i only after product (2) of tile i, issued earlier, has read it.
+    if (lane == 0) {
+      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;   // 0 = f16, 1 = bf16
+      const uint32_t idesc_k = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t basis_addr = smem_u32(sm.basis);
+      for (int i = 0; i <= n_stages; ++i) {
+        if (i < n_stages) {
+          const int buf = i % NBUF_A;
+          if (!mbar_wait_thread(smem_u32(&sm.a_full[buf]), (uint32_t)((i / NBUF_A) & 1), abort_flag)) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sm.a_tile[buf]);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            // A: K-major, 8-row core matrices 128 B apart (SBO), the two 8-coefficient chunks 2048 B apart (LBO)
+            // B: MN-major, 8-column core matrices 128 B apart (SBO), the two 8-row groups 2048 B apart (LBO)
+            umma_f16(tmem_base + TM_K + buf * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
+                     umma_desc(basis_addr + ks * 4096, 2048, 128), idesc_k, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&sm.t_ready[buf]));
+          umma_commit(smem_u32(&sm.a_free[buf]));
+        }
+        if (i >= 1) {
+          const int c = i - 1, grp = c & 1, slot = c % NQ;
+          if (!mbar_wait_thread(smem_u32(&sm.kp_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
+          if (!mbar_wait_thread(smem_u32(&sm.q_full[slot]), (uint32_t)((c / NQ) & 1), abort_flag)) break;
+          tc_fence_after();
+          const uint32_t q_addr = smem_u32(sm.qrot[slot]);
+          const uint32_t kp = tmem_base + TM_K + grp * 128;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            // A: K' of the tile, dims 16ks..16ks+15 = packed columns 8ks.. (dims < 64) or 64 + 8(ks-4).. (dims >= 64)
+            // B: K-major, head rows 16 B apart inside a core matrix, 8-row groups 128 B (SBO), dim chunks Q_LBO apart
+            umma_f16_ta(tmem_base + TM_S + 16 * grp, kp + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4)),
+                        umma_desc(q_addr + ks * 2 * Q_LBO, Q_LBO, 128), idesc_s, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&sm.s_ready[grp]));
+          umma_commit(smem_u32(&sm.q_free[slot]));
+        }
+      }
+    }
+  }
+
+  else if (warp == W_PV) {
+    // =========================== tensor-core issuer 2: product (3) ===========================
+    // A thread of its own, so that waiting for a group's softmax never holds back products (1) and (2).
+    if (lane == 0) {
+      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+      int row_pv = row0;
+      for (int c = 0; c < n_stages; ++c) {
+        const int grp = c & 1, vb = c % NBUF_V;
+        if (!mbar_wait_thread(smem_u32(&sm.p_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
+        if (!mbar_wait_thread(smem_u32(&sm.v_full[vb]), (uint32_t)((c / NBUF_V) & 1), abort_flag)) break;
+        tc_fence_after();
+        const int u = u_begin + c;
+        while (u >= sm.prefix[row_pv + 1]) ++row_pv;
+        const int c_row_lo = max(sm.prefix[row_pv], u_begin) - u_begin;
+        const bool first = (c - c_row_lo) < NGROUP;   // the group's first tile of this row starts a new sum
+        const uint32_t v_addr = smem_u32(sm.v_tile[vb]), p_addr = smem_u32(sm.p_tile[grp]);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          // A: K-major, 8-row core matrices 128 B apart (SBO), the two 8-coefficient chunks 2048 B apart (LBO)
-          // B: MN-major, 8-column core matrices 128 B apart (SBO), the two 8-row groups 2048 B apart (LBO)
-          umma_f16(tmem_base + buf * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
-                   umma_desc(basis_addr + ks * 4096, 2048, 128), idesc, ks > 0 ? 1u : 0u);
+          // A = XV^T: MN-major, 16 tokens per step (256 B), token groups of 8 are 128 B apart (LBO), latent
+          //     chunks 2048 B apart (SBO)
+          // B = P:    MN-major, token groups of 8 are 128 B apart (LBO); the second group of 8 columns aliases
+          //     the first (SBO 0): columns 8..15 of the result duplicate 0..7 and are never read
+          umma_f16(tmem_base + TM_O + 16 * grp, umma_desc(v_addr + ks * 256, 128, 2048),
+                   umma_desc(p_addr + ks * 256, 128, 0), idesc_o, (ks > 0 || !first) ? 1u : 0u);
         }
-        umma_commit(smem_u32(&sm.t_ready[buf]));
-        umma_commit(smem_u32(&sm.a_free[buf]));
+        umma_commit(smem_u32(&sm.pv_done[grp]));
+        umma_commit(smem_u32(&sm.v_free[vb]));
       }
-      __syncwarp();
     }
   }
+
   else if (warp < NCW) {
-  // ============================= consumer warps =============================
-  // Consumer warp w owns the 16-token group gi = 2*(w&3) + (w>>2) of every stage: those are the tensor-memory
-  // lanes 32*(w&3) + 16*(w>>2) .. +15, the only ones a warp in SM sub-partition w&3 may read.
-  const int gi = 2 * (warp & 3) + (warp >> 2);
-  const uint32_t tmem_lane = (uint32_t)(16 * gi) << 16;
-  const int gq = lane >> 2, qq = lane & 3;
-  const uint32_t zero_addr = smem_u32(sm.zero_chunk);
-  const float4* trig4 = sm.trig;
+  // ============================= token warps =============================
+  // Group grp = warp / 4 takes the tiles of parity grp.  Thread (wq, lane) owns token 32 wq + lane of each of
+  // them, which is tensor-memory lane 32 wq + lane -- the lanes a warp in SM sub-partition wq may access.
+  const int grp = warp >> 2, wq = warp & 3;
+  const int tok = 32 * wq + lane;
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * wq) << 16);
+  const uint32_t k_addr = lane_addr + TM_K + 128 * grp;
+  const uint32_t s_addr = lane_addr + TM_S + 16 * grp + 4 * wq;   // this quarter's columns: n = 4 wq + head
+  const uint32_t o_addr = lane_addr + TM_O + 16 * grp;
 
   int row = row0;
-  int c = 0;                  // next stage
   while (row < p.batch && sm.prefix[row] < u_end) {
-    const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;   // stages of this row: [.., c_hi)
-    float m_run0 = -INFINITY, m_run1 = -INFINITY, l_part0 = 0.f, l_part1 = 0.f;   // heads 2qq, 2qq+1
-    float oacc[8][4];
+    const int c_lo = max(sm.prefix[row], u_begin) - u_begin;     // tiles of this row in this CTA: [c_lo, c_hi)
+    const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;
+    float m_ref[HP], l_part[HP];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+    for (int h = 0; h < HP; ++h) { m_ref[h] = -INFINITY; l_part[h] = 0.f; }
+    int k_last = -1;            // this group's last tile of the row (index in the group's own tile sequence)
+    bool dead = false;
 
-    for (; c < c_hi; ++c) {
-      const int slot = c % NSLOT, buf = c % NBUF;
-      if (*abort_flag) continue;
-      const uint32_t phase = (uint32_t)((c / NSLOT) & 1);
-      if (!mbar_wait(smem_u32(&sm.full_k[slot]), phase, abort_flag)) continue;
-      // lengths as the gather warps left them (0 = token absent or rejected)
-      const int klen = sm.meta[0][c % MSLOT].lens[gi * 16 + (lane & 15)];   // lanes 16..31 mirror lanes 0..15
-      const uint32_t valid = __ballot_sync(0xffffffffu, klen > 0) & 0xffffu;
-      // the stage's K tile in tensor memory
-      if (!mbar_wait(smem_u32(&sm.t_ready[buf]), (uint32_t)((c / NBUF) & 1), abort_flag)) continue;
+    for (int c = c_lo + (((c_lo & 1) != grp) ? 1 : 0); c < c_hi; c += NGROUP) {
+      if (dead || *abort_flag) { dead = true; continue; }
+      const int k = c >> 1;                       // tile count of this group, CTA-wide
+      const uint32_t par = (uint32_t)(k & 1);
+      const bool first = (c - c_lo) < NGROUP;     // O holds nothing of this row yet
+      if (!mbar_wait(smem_u32(&sm.t_ready[grp]), par, abort_flag)) { dead = true; continue; }
       tc_fence_after();
-      const uint32_t tmem_tile = tmem_base + tmem_lane + buf * 128;
-      if (valid == 0u) {
-        tc_fence_before();
-        if (lane == 0) mbar_arrive(smem_u32(&sm.t_free[buf]));
-      }
-      if (valid != 0u) {
-        // ---------------- K from tensor memory, RoPE, S = K' . Q~^T : two passes over half of the head dims ----------------
-        // Pass h handles dims [32h, 32h+32) and their rotation partners [64+32h, 64+32h+32): only 32 accumulator
-        // registers are live at a time (this is what lets 16 warps fit on the SM).
-        const uint32_t qbase = smem_u32(sm.qrot[slot][gi / (QSUB / 16)]);
-        const int qr = lane & 7;   // ldmatrix rows 0..HP-1 = heads, the other rows read the zero chunk
-        const uint32_t qaddr = (qr < HP) ? qbase + qr * Q_PITCH + (lane >> 3) * 16 : zero_addr;
-        const int tA = (gi & (QSUB / 16 - 1)) * 16 + gq, tB = tA + 8;   // offsets inside the 64-token sub-stage
-        float sacc[4] = {0.f, 0.f, 0.f, 0.f}, sacc2[4] = {0.f, 0.f, 0.f, 0.f};   // two chains: low dims / partners
-        float ss0 = 0.f, ss1 = 0.f;     // sum of squares of the two token rows (K-RMSNorm)
+      // ---------------- K row from tensor memory: [RMSNorm,] RoPE, K' back as packed 16-bit pairs ----------------
+      float ss = 0.f;
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          // this group's K rows, dims [32hf, 32hf+32) and their rotation partners [64+32hf, ..): acc[0..3] =
-          // n-tiles 4hf+i (dims j), acc[4..7] = n-tiles 8+4hf+i (dims j+64), in the mma.sync accumulator layout
-          float acc[8][4];
-          tmem_ld_2x_16x32(acc, tmem_tile + 32 * hf, tmem_tile + 64 + 32 * hf);
-          if (hf == 1) {   // both halves are in registers: the accumulator buffer may be overwritten
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm.t_free[buf]));
-          }
-          if (KNORM) {
-            // RMSNorm of K (Qwen3): the weight is applied here, the per-token 1/rms scales the score at the end
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              ss0 = fmaf(acc[i][0], acc[i][0], fmaf(acc[i][1], acc[i][1], ss0));
-              ss1 = fmaf(acc[i][2], acc[i][2], fmaf(acc[i][3], acc[i][3], ss1));
-              const int nt = (i >> 2) * 8 + 4 * hf + (i & 3);
-              const float2 w = *reinterpret_cast<const float2*>(&sm.knorm_w[8 * nt + 2 * qq]);
-              acc[i][0] *= w.x; acc[i][1] *= w.y; acc[i][2] *= w.x; acc[i][3] *= w.y;
-            }
-          }
-          // local RoPE on packed fp32 pairs, packed to 16-bit A fragments
-          uint32_t kl[4][2], kh[4][2];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int nt = 4 * hf + i;
-            const float4 ta = trig4[(tA * 8 + (nt ^ (tA & 7))) * 4 + qq];   // {c_j, c_j+1, s_j, s_j+1}
-            const float4 tb = trig4[(tB * 8 + (nt ^ (tB & 7))) * 4 + qq];
-            {
-              const float2 lo = make_float2(acc[i][0], acc[i][1]), hi = make_float2(acc[4 + i][0], acc[4 + i][1]);
-              const float2 C = make_float2(ta.x, ta.y), S = make_float2(ta.z, ta.w);
-              const float2 u = __fmul2_rn(hi, S);
-              const float2 lo2 = __ffma2_rn(lo, C, make_float2(-u.x, -u.y));
-              const float2 hi2 = __ffma2_rn(lo, S, __fmul2_rn(hi, C));
-              kl[i][0] = Mma<T>::pack(lo2.x, lo2.y);
-              kh[i][0] = Mma<T>::pack(hi2.x, hi2.y);
-            }
-            {
-              const float2 lo = make_float2(acc[i][2], acc[i][3]), hi = make_float2(acc[4 + i][2], acc[4 + i][3]);
-              const float2 C = make_float2(tb.x, tb.y), S = make_float2(tb.z, tb.w);
-              const float2 u = __fmul2_rn(hi, S);
-              const float2 lo2 = __ffma2_rn(lo, C, make_float2(-u.x, -u.y));
-              const float2 hi2 = __ffma2_rn(lo, S, __fmul2_rn(hi, C));
-              kl[i][1] = Mma<T>::pack(lo2.x, lo2.y);
-              kh[i][1] = Mma<T>::pack(hi2.x, hi2.y);
-            }
-          }
-          // S[tokens x heads] += K'[:, these dims] . Q~^T : the rotated fragments are the A operand, the rotated
-          // queries the B operand.  16-dim steps 2hf, 2hf+1 (low dims) and 4+2hf, 4+2hf+1 (partners).
-          uint32_t ql[4], qh[4];
-          ldsm_x4(ql, (qr < HP) ? qaddr + hf * 64 : zero_addr);         // {step 2hf: dims 0-7, 8-15 ; step 2hf+1: ...}
-          ldsm_x4(qh, (qr < HP) ? qaddr + (2 + hf) * 64 : zero_addr);
-          Mma<T>::run(sacc, kl[0][0], kl[0][1], kl[1][0], kl[1][1], ql[0], ql[1]);
-          Mma<T>::run(sacc, kl[2][0], kl[2][1], kl[3][0], kl[3][1], ql[2], ql[3]);
-          Mma<T>::run(sacc2, kh[0][0], kh[0][1], kh[1][0], kh[1][1], qh[0], qh[1]);
-          Mma<T>::run(sacc2, kh[2][0], kh[2][1], kh[3][0], kh[3][1], qh[2], qh[3]);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sacc[i] += sacc2[i];
+      for (int i = 0; i < 8; ++i) {
+        // pairs j = 8i..8i+7: dims j (columns 8i..) and j+64 (columns 64+8i..); table cells 16i..: per two pairs
+        // {cos_j, cos_j+1, sin_j, sin_j+1}
+        float lo[8], hi[8], tg[16];
+        tmem_ld_rope_chunk(lo, hi, tg, k_addr + 8 * i, k_addr + 64 + 8 * i, lane_addr + TM_TRIG + 16 * i);
         if (KNORM) {
-          ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
-          ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
-          const float rs0 = rsqrtf(ss0 * (1.0f / D) + p.k_norm_eps), rs1 = rsqrtf(ss1 * (1.0f / D) + p.k_norm_eps);
-          sacc[0] *= rs0; sacc[1] *= rs0; sacc[2] *= rs1; sacc[3] *= rs1;
-        }
-        // ---------------- V fragments: fetched now, used after the softmax ----------------
-        const bool v_ok = mbar_wait(smem_u32(&sm.full_v[slot]), phase, abort_flag);
-        uint32_t va[8][4];
-        int vmax = 0;
-        if (v_ok) {
-          const StageHdr hv = sm.hdr[slot];
-          const StageMeta& mv = sm.meta[1][c % MSLOT];
-          const int tv = gi * 16 + (lane & 7) + 8 * (lane >> 4);   // token whose row this lane addresses
-          int vlen_t = 0;
-          uint32_t vrow = zero_addr;
-          if (tv < hv.n_tok) {
-            vlen_t = mv.lens[tv];
-            const int vo = mv.offs[tv] - hv.start;
-            if (((vlen_t | vo) & 7) != 0 || vlen_t < 0 || vlen_t > R || vo < 0 || vo + vlen_t > hv.elems) {
-              set_status(p.status, DKV_ST_BAD_LENGTH);
-              vlen_t = 0;
-            }
-            vrow = hv.base + ((uint32_t)vo >> 3) * 16u;
-          }
-          vmax = __reduce_max_sync(0xffffffffu, vlen_t);
-          const int cpar = (lane >> 3) & 1;
+          // RMSNorm of K (Qwen3): the weight is applied here, the per-token 1/rms scales the score later
+          const float4 w0 = *reinterpret_cast<const float4*>(&sm.knorm_w[8 * i]);
+          const float4 w1 = *reinterpret_cast<const float4*>(&sm.knorm_w[8 * i + 4]);
+          const float4 w2 = *reinterpret_cast<const float4*>(&sm.knorm_w[64 + 8 * i]);
+          const float4 w3 = *reinterpret_cast<const float4*>(&sm.knorm_w[64 + 8 * i + 4]);
+          const float wl[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          const float wh[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
 #pragma unroll
-          for (int mt = 0; mt < 8; ++mt) {
-            if (mt * 16 < vmax) {
-              const int chunk = 2 * mt + cpar;
-              ldsm_x4_t(va[mt], (chunk * 8 < vlen_t) ? vrow + chunk * 16 : zero_addr);
-            }
+          for (int e = 0; e < 8; ++e) {
+            ss = fmaf(lo[e], lo[e], fmaf(hi[e], hi[e], ss));
+            lo[e] *= wl[e];
+            hi[e] *= wh[e];
           }
         }
-        // ---------------- online softmax (base 2) ----------------
-        // this lane: tokens gq and gq+8, heads 2qq and 2qq+1; head maxima are reduced over the 8 token lanes
-        float sc0 = sacc[0], sc1 = sacc[1], sc2 = sacc[2], sc3 = sacc[3];
-        if (!((valid >> gq) & 1u)) { sc0 = -INFINITY; sc1 = -INFINITY; }
-        if (!((valid >> (gq + 8)) & 1u)) { sc2 = -INFINITY; sc3 = -INFINITY; }
-        float mx0 = fmaxf(sc0, sc2), mx1 = fmaxf(sc1, sc3);
+        uint32_t plo[4], phi[4];
 #pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
-          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+        for (int m = 0; m < 4; ++m) {
+          const float2 L = make_float2(lo[2 * m], lo[2 * m + 1]), H = make_float2(hi[2 * m], hi[2 * m + 1]);
+          const float2 C = make_float2(tg[4 * m], tg[4 * m + 1]), S = make_float2(tg[4 * m + 2], tg[4 * m + 3]);
+          const float2 u = __fmul2_rn(H, S);
+          const float2 lo2 = __ffma2_rn(L, C, make_float2(-u.x, -u.y));
+          const float2 hi2 = __ffma2_rn(L, S, __fmul2_rn(H, C));
+          plo[m] = Pack<T>::two(lo2.x, lo2.y);
+          phi[m] = Pack<T>::two(hi2.x, hi2.y);
         }
-        const float mn0 = fmaxf(m_run0, mx0), mn1 = fmaxf(m_run1, mx1);
-        const float al0 = exp2f(m_run0 - mn0), al1 = exp2f(m_run1 - mn1);
-        const float p0 = exp2f(sc0 - mn0), p1 = exp2f(sc1 - mn1), p2 = exp2f(sc2 - mn0), p3 = exp2f(sc3 - mn1);
-        l_part0 = l_part0 * al0 + (p0 + p2);
-        l_part1 = l_part1 * al1 + (p1 + p3);
-        m_run0 = mn0; m_run1 = mn1;
-        // P[tokens x heads] -> B operand [token pairs x head] by an 8x8 transpose per token half
-        const uint32_t pb0 = movmatrix_t(Mma<T>::pack(p0, p1)), pb1 = movmatrix_t(Mma<T>::pack(p2, p3));
-        if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { oacc[i][0] *= al0; oacc[i][1] *= al1; oacc[i][2] *= al0; oacc[i][3] *= al1; }
-        }
-        // ---------------- O^T[r x heads] += XV^T . P ----------------
-#pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-          if (mt * 16 < vmax) Mma<T>::run(oacc[mt], va[mt][0], va[mt][1], va[mt][2], va[mt][3], pb0, pb1);
-        }
-      } else {
-        // nothing to do for this group, but its V bytes must have landed before the slot is handed back
-        mbar_wait(smem_u32(&sm.full_v[slot]), phase, abort_flag);
+        // packed columns 4i.. (dims 8i..8i+7) and 64+4i.. (dims 64+8i..): both lie inside columns already read
+        tmem_st4(k_addr + 4 * i, plo[0], plo[1], plo[2], plo[3]);
+        tmem_st4(k_addr + 64 + 4 * i, phi[0], phi[1], phi[2], phi[3]);
       }
+      tmem_wait_st();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.empty_bar[slot]));
+      if (lane == 0) mbar_arrive(smem_u32(&sm.kp_ready[grp]));
+
+      // ---------------- scores of this token for the group's heads ----------------
+      if (!mbar_wait(smem_u32(&sm.s_ready[grp]), par, abort_flag)) { dead = true; continue; }
+      tc_fence_after();
+      float s[HP];
+      tmem_ld4(s, s_addr);
+      if (KNORM) {
+        const float rs = rsqrtf(ss * (1.0f / D) + p.k_norm_eps);
+#pragma unroll
+        for (int h = 0; h < HP; ++h) s[h] *= rs;
+      }
+      const bool valid = (sm.kvalid[c % KV_RING][wq] >> lane) & 1u;
+      float mx[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        if (!valid) s[h] = -INFINITY;
+        mx[h] = warp_max_redux(s[h]);
+      }
+      // tile maxima: the four warps of the group meet on an mbarrier (bounded wait, unlike a named barrier)
+      if (lane == 0) {
+        *reinterpret_cast<float4*>(sm.tmax[grp][par][wq]) = make_float4(mx[0], mx[1], mx[2], mx[3]);
+        mbar_arrive(smem_u32(&sm.grp_sync[grp]));
+      }
+      if (!mbar_wait(smem_u32(&sm.grp_sync[grp]), par, abort_flag)) { dead = true; continue; }
+      float factor[HP];
+      bool grow = false;
+      {
+        const float4 t0 = *reinterpret_cast<const float4*>(sm.tmax[grp][par][0]);
+        const float4 t1 = *reinterpret_cast<const float4*>(sm.tmax[grp][par][1]);
+        const float4 t2 = *reinterpret_cast<const float4*>(sm.tmax[grp][par][2]);
+        const float4 t3 = *reinterpret_cast<const float4*>(sm.tmax[grp][par][3]);
+        const float tm[HP] = {fmaxf(fmaxf(t0.x, t1.x), fmaxf(t2.x, t3.x)), fmaxf(fmaxf(t0.y, t1.y), fmaxf(t2.y, t3.y)),
+                              fmaxf(fmaxf(t0.z, t1.z), fmaxf(t2.z, t3.z)), fmaxf(fmaxf(t0.w, t1.w), fmaxf(t2.w, t3.w))};
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          factor[h] = 1.f;
+          if (tm[h] > m_ref[h] + M_SLACK) {   // also the first tile with a token: -inf + slack = -inf
+            factor[h] = exp2f(m_ref[h] - tm[h]);   // 0 when there was no reference yet
+            m_ref[h] = tm[h];
+            grow = true;
+          }
+        }
+      }
+      // product (3) of the group's previous tile must be complete before P is overwritten or O rescaled
+      if (k >= 1 && !mbar_wait(smem_u32(&sm.pv_done[grp]), (uint32_t)((k - 1) & 1), abort_flag)) { dead = true; continue; }
+      if (grow) {   // uniform over the group: every thread sees the same maxima
+#pragma unroll
+        for (int h = 0; h < HP; ++h) l_part[h] *= factor[h];
+        if (!first) {
+          tc_fence_after();
+          float o[4];
+          tmem_ld4(o, o_addr);
+          tmem_st4(o_addr, __float_as_uint(o[0] * factor[0]), __float_as_uint(o[1] * factor[1]),
+                   __float_as_uint(o[2] * factor[2]), __float_as_uint(o[3] * factor[3]));
+          tmem_wait_st();
+        }
+      }
+      float pr[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        pr[h] = exp2f(s[h] - (m_ref[h] == -INFINITY ? 0.f : m_ref[h]));
+        l_part[h] += pr[h];
+      }
+      *reinterpret_cast<uint4*>(sm.p_tile[grp] + tok * 16) = make_uint4(Pack<T>::two(pr[0], pr[1]), Pack<T>::two(pr[2], pr[3]), 0u, 0u);
+      proxy_fence_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[grp]));
+      k_last = k;
     }
 
-    // ---------------- row flush: merge the consumer warps' partial states ----------------
+    // ---------------- row flush: the two groups' partial states are merged ----------------
+    {
+      float o[4] = {0.f, 0.f, 0.f, 0.f};
+      if (k_last >= 0 && !dead && mbar_wait(smem_u32(&sm.pv_done[grp]), (uint32_t)(k_last & 1), abort_flag)) {
+        tc_fence_after();
+        tmem_ld4(o, o_addr);   // O^T[r = tok][head]
+      }
 #pragma unroll
-    for (int o = 4; o < 32; o <<= 1) {
-      l_part0 += __shfl_xor_sync(0xffffffffu, l_part0, o);
-      l_part1 += __shfl_xor_sync(0xffffffffu, l_part1, o);
-    }
-    if (gq == 0) {
-      if (2 * qq < HP) { sm.merge[warp][2 * qq][0] = m_run0; sm.merge[warp][2 * qq][1] = l_part0; }
-      if (2 * qq + 1 < HP) { sm.merge[warp][2 * qq + 1][0] = m_run1; sm.merge[warp][2 * qq + 1][1] = l_part1; }
-    }
-#pragma unroll
-    for (int mt = 0; mt < 8; ++mt) {
-      const int r = 16 * mt + gq;
-      if (2 * qq < HP) { sm.merge[warp][2 * qq][2 + r] = oacc[mt][0]; sm.merge[warp][2 * qq][2 + r + 8] = oacc[mt][2]; }
-      if (2 * qq + 1 < HP) { sm.merge[warp][2 * qq + 1][2 + r] = oacc[mt][1]; sm.merge[warp][2 * qq + 1][2 + r + 8] = oacc[mt][3]; }
+      for (int h = 0; h < HP; ++h) {
+        sm.merge[grp][h][2 + tok] = o[h];
+        const float l = warp_sum(l_part[h]);
+        if (lane == 0) sm.lsum[grp][wq][h] = l;
+      }
+      if (wq == 0 && lane < HP) sm.merge[grp][lane][0] = m_ref[lane];
     }
     consumer_bar();
     const int b = p.batch_index ? p.batch_index[row] : row;
-    const int ctid = tid;  // consumer threads come first in the block
+    const int ctid = tid;  // token threads come first in the block
     constexpr int N_ITEMS = HP * 128, N_IT = (N_ITEMS + NCW * 32 - 1) / (NCW * 32);
     float outv[N_IT], L_tot[N_IT], M_tot[N_IT];
 #pragma unroll
@@ -900,14 +817,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const int h = item >> 7, r = item & 127;
       float M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < NCW; ++w) M = fmaxf(M, sm.merge[w][h][0]);
+      for (int w = 0; w < NGROUP; ++w) M = fmaxf(M, sm.merge[w][h][0]);
       float v = 0.f, L = 0.f;
 #pragma unroll
-      for (int w = 0; w < NCW; ++w) {
+      for (int w = 0; w < NGROUP; ++w) {
         const float mw = sm.merge[w][h][0];
         const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        const float lw = (sm.lsum[w][0][h] + sm.lsum[w][1][h]) + (sm.lsum[w][2][h] + sm.lsum[w][3][h]);
         v = fmaf(sm.merge[w][h][2 + r], wgt, v);
-        L = fmaf(sm.merge[w][h][1], wgt, L);
+        L = fmaf(lw, wgt, L);
       }
       outv[it] = v; L_tot[it] = L; M_tot[it] = M;
     }
@@ -953,7 +871,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
     ++row;
   }
-  }   // consumer warps
+  }   // token warps
 
   // ---- epilogue: every warp arrives here; the tensor memory is returned by the warp that allocated it ----
   tc_fence_before();
@@ -1098,20 +1016,15 @@ static int launch_mma(const dkv_attn_args* a, int n_cta) {
   const float log_theta = (float)log((double)a->theta);
   const size_t smem = smem_bytes();
   dim3 grid(FUSED ? a->batch : n_cta, a->n_basis_groups);
-  // metadata rows that start on 16-byte boundaries are staged with 16-byte async copies
-  auto al16 = [](const dkv_side& s) {
-    return (((uintptr_t)s.lens | (uintptr_t)s.offs) & 15) == 0 && (s.lens_stride_a & 3) == 0 && (s.offs_stride_a & 3) == 0;
-  };
-  const int meta16 = al16(a->k) && al16(a->v) ? 1 : 0;
   cudaError_t e;
   if (a->k_norm_weight) {
     auto kern = mma_decode_kernel<T, FUSED, true>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta, meta16);
+    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta);
   } else {
     auto kern = mma_decode_kernel<T, FUSED, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta, meta16);
+    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta);
   }
   DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
   DKV_CHECK_LAUNCH();

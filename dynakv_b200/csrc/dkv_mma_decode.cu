@@ -9,11 +9,11 @@
 // of the tile (tensor-memory lane = token), so neither RoPE nor the softmax needs a shuffle:
 //   2+2 gather warps : copy each token's ragged K / V coefficient row (16-byte cp.async, zero fill past the
 //                      row's length) into K-major, unswizzled 128 x 128 operand tiles in shared memory;
-//   2 MMA threads    : per tile  (1) K = X . Bk          M=128 tokens, N=128, K=128 (A, B from shared memory)
+//   1 MMA thread     : per tile  (1) K = X . Bk          M=128 tokens, N=128, K=128 (A, B from shared memory)
 //                                (2) S = K' . Q~^T       M=128 tokens, N=16,  K=128 (A = K' in tensor memory)
 //                                (3) O^T += XV^T . P     M=128 latent, N=16,  K=128 tokens (accumulates per row);
 //                      completion of each product is signalled by tcgen05.commit on mbarriers;
-//   1 rotator warp   : Q~ = scale . R(-s) q for the four 32-token quarters of a tile (the B operand of (2)),
+//   2 rotator warps  : Q~ = scale . R(-s) q for the four 32-token quarters of a tile (the B operand of (2)),
 //                      so token threads rotate K only by their local offset 0..31;
 //   2 x 4 token warps: group g takes tiles of parity g.  A thread reads its token's K row from tensor memory
 //                      (tcgen05.ld.32x32b), applies [RMSNorm and] RoPE in fp32 with its 64 (cos, sin) pairs,
@@ -40,7 +40,7 @@ constexpr int W_ROT = 8;               // query rotator
 constexpr int W_MMA = 9;               // tcgen05.mma issuer, owns the tensor-memory allocation
 constexpr int W_KG0 = 10;              // K gather warps 10, 11 (64 tokens of the tile each)
 constexpr int W_VG0 = 12;              // V gather warps 12, 13
-constexpr int W_PV = 14;               // second tcgen05.mma issuer: product (3)
+constexpr int W_ROT2 = 14;             // second query rotator (quarters 2, 3 of each tile)
 constexpr int NTHREADS = 16 * 32;      // warp 15 is idle; 128 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
 constexpr int QSUB = 32;               // tokens per query-rotation quarter (= one token warp)
@@ -127,6 +127,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
   ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+// Non-blocking probe of a barrier phase.
+__device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
   return ok != 0;
 }
 // The same for a single thread (the tensor-core issuers run on one lane).
@@ -305,7 +315,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       sm.abort_flag = 0;
       for (int s = 0; s < NBUF_A; ++s) { mbar_init(smem_u32(&sm.a_full[s]), 2); mbar_init(smem_u32(&sm.a_free[s]), 1); }
       for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 2); mbar_init(smem_u32(&sm.v_free[s]), 1); }
-      for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 1); mbar_init(smem_u32(&sm.q_free[s]), 1); }
+      for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 2); mbar_init(smem_u32(&sm.q_free[s]), 1); }
       for (int s = 0; s < NGROUP; ++s) {
         mbar_init(smem_u32(&sm.t_ready[s]), 1);
         mbar_init(smem_u32(&sm.kp_ready[s]), 4);
@@ -423,16 +433,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     ri.first_unit = sm.prefix[ri.row];
   };
 
-  if (warp == W_ROT) {
+  if (warp == W_ROT || warp == W_ROT2) {
     // =========================== query rotator warp ===========================
-    // For the four 32-token quarters of every tile (base position s) it publishes Q~ = scale * R(-s) q for the
-    // group's heads as row n = 4*quarter + head of the B operand of product (2), so that
-    // q~ . R(t) k = q . R(s + t) k with the local offset t = 0..31.  Lane l owns the pairs j = 2l, 2l+1.
+    // For the four 32-token quarters of every tile (base position s) the two rotator warps (quarters 0,1 and
+    // 2,3) publish Q~ = scale * R(-s) q for the group's heads as row n = 4*quarter + head of the B operand of
+    // product (2), so that q~ . R(t) k = q . R(s + t) k with the local offset t = 0..31.  Lane l owns the pairs
+    // j = 2l, 2l+1.
     const float f0 = expf(-((float)(4 * lane) / (float)D) * log_theta);
     const float f1 = expf(-((float)(4 * lane + 2) / (float)D) * log_theta);
-    float cd0, sd0, cd1, sd1;
+    const int qt0 = (warp == W_ROT) ? 0 : 2;          // this warp's first quarter
+    float cd0, sd0, cd1, sd1, ct0, st0, ct1, st1;     // rotation by one quarter / by the three quarters to the next tile
     sincosf((float)QSUB * f0, &sd0, &cd0);
     sincosf((float)QSUB * f1, &sd1, &cd1);
+    sincosf((float)(ST_TOK - QSUB) * f0, &st0, &ct0);
+    sincosf((float)(ST_TOK - QSUB) * f1, &st1, &ct1);
     const float qscale = rsqrtf((float)D) * 1.4426950408889634f;  // softmax scale and log2(e) folded into q
     float a0[HP], b0[HP], a1[HP], b1[HP];   // (q~_j, q~_{j+64}) for j = 2l and j = 2l+1
     int row = row0;
@@ -446,11 +460,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const int s0 = (u - sm.prefix[row]) * ST_TOK;
       unsigned char* const qt_base = sm.qrot[slot] + (lane >> 2) * Q_LBO + (lane & 3) * 4;
 #pragma unroll
-      for (int qt = 0; qt < ST_TOK / QSUB; ++qt) {
-        if (row_start && qt == 0) {
+      for (int qq = 0; qq < 2; ++qq) {
+        const int qt = qt0 + qq;
+        if (row_start && qq == 0) {
           float sa, ca, sb, cb;
-          sincosf((float)s0 * f0, &sa, &ca);
-          sincosf((float)s0 * f1, &sb, &cb);
+          sincosf((float)(s0 + qt0 * QSUB) * f0, &sa, &ca);
+          sincosf((float)(s0 + qt0 * QSUB) * f1, &sb, &cb);
 #pragma unroll
           for (int h = 0; h < HP; ++h) {
             float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
@@ -463,11 +478,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
             a1[h] = y0 * cb + y1 * sb; b1[h] = y1 * cb - y0 * sb;
           }
         } else {
+          // from this warp's previous quarter: one quarter on (qq == 1) or three quarters on (next tile)
+          const float c0 = qq ? cd0 : ct0, s0r = qq ? sd0 : st0, c1 = qq ? cd1 : ct1, s1r = qq ? sd1 : st1;
 #pragma unroll
           for (int h = 0; h < HP; ++h) {
             const float x0 = a0[h], x1 = b0[h], y0 = a1[h], y1 = b1[h];
-            a0[h] = x0 * cd0 + x1 * sd0; b0[h] = x1 * cd0 - x0 * sd0;
-            a1[h] = y0 * cd1 + y1 * sd1; b1[h] = y1 * cd1 - y0 * sd1;
+            a0[h] = x0 * c0 + x1 * s0r; b0[h] = x1 * c0 - x0 * s0r;
+            a1[h] = y0 * c1 + y1 * s1r; b1[h] = y1 * c1 - y0 * s1r;
           }
         }
 #pragma unroll
@@ -569,20 +586,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   }
 
   else if (warp == W_MMA) {
-    // =========================== tensor-core issuer 1: products (1) and (2) ===========================
-    // One lane runs the whole loop.  Step i issues product (1) of tile i, then product (2) of tile i-1, each
-    // after the barriers that say its operands are in place.  The tensor core executes one thread's
-    // instructions in issue order, which also orders the re-use of the accumulator buffers: tile i+2 overwrites
-    // K' of tile i only after product (2) of tile i, issued earlier, has read it.
+    // =========================== tensor-core issuer ===========================
+    // One lane issues all three products.  It never blocks on one barrier: it probes, in turn, whether the next
+    // product (1), (2) or (3) has its operands in place and issues what is ready, so that waiting for one
+    // group's softmax does not hold back the other group's products.  The tensor core executes this thread's
+    // instructions in issue order, which also orders the re-use of the accumulator buffers: product (1) of tile
+    // i+2 is only issued after product (2) of tile i, which reads K' from the same buffer.
     if (lane == 0) {
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;   // 0 = f16, 1 = bf16
       const uint32_t idesc_k = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t basis_addr = smem_u32(sm.basis);
-      for (int i = 0; i <= n_stages; ++i) {
-        if (i < n_stages) {
-          const int buf = i % NBUF_A;
-          if (!mbar_wait_thread(smem_u32(&sm.a_full[buf]), (uint32_t)((i / NBUF_A) & 1), abort_flag)) break;
+      int ri = 0, qi = 0, pi = 0;     // next tile of products (1), (2), (3)
+      int row_pv = row0;
+      uint32_t idle = 0;
+      while (pi < n_stages) {
+        bool progress = false;
+        if (ri < n_stages && ri - qi < NBUF_A && mbar_probe(smem_u32(&sm.a_full[ri % NBUF_A]), (uint32_t)((ri / NBUF_A) & 1))) {
+          const int buf = ri % NBUF_A;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sm.a_tile[buf]);
 #pragma unroll
@@ -594,11 +616,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           }
           umma_commit(smem_u32(&sm.t_ready[buf]));
           umma_commit(smem_u32(&sm.a_free[buf]));
+          ++ri;
+          progress = true;
         }
-        if (i >= 1) {
-          const int c = i - 1, grp = c & 1, slot = c % NQ;
-          if (!mbar_wait_thread(smem_u32(&sm.kp_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
-          if (!mbar_wait_thread(smem_u32(&sm.q_full[slot]), (uint32_t)((c / NQ) & 1), abort_flag)) break;
+        if (qi < ri && mbar_probe(smem_u32(&sm.kp_ready[qi & 1]), (uint32_t)((qi >> 1) & 1)) &&
+            mbar_probe(smem_u32(&sm.q_full[qi % NQ]), (uint32_t)((qi / NQ) & 1))) {
+          const int grp = qi & 1, slot = qi % NQ;
           tc_fence_after();
           const uint32_t q_addr = smem_u32(sm.qrot[slot]);
           const uint32_t kp = tmem_base + TM_K + grp * 128;
@@ -611,39 +634,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           }
           umma_commit(smem_u32(&sm.s_ready[grp]));
           umma_commit(smem_u32(&sm.q_free[slot]));
+          ++qi;
+          progress = true;
         }
-      }
-    }
-  }
-
-  else if (warp == W_PV) {
-    // =========================== tensor-core issuer 2: product (3) ===========================
-    // A thread of its own, so that waiting for a group's softmax never holds back products (1) and (2).
-    if (lane == 0) {
-      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-      const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-      int row_pv = row0;
-      for (int c = 0; c < n_stages; ++c) {
-        const int grp = c & 1, vb = c % NBUF_V;
-        if (!mbar_wait_thread(smem_u32(&sm.p_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
-        if (!mbar_wait_thread(smem_u32(&sm.v_full[vb]), (uint32_t)((c / NBUF_V) & 1), abort_flag)) break;
-        tc_fence_after();
-        const int u = u_begin + c;
-        while (u >= sm.prefix[row_pv + 1]) ++row_pv;
-        const int c_row_lo = max(sm.prefix[row_pv], u_begin) - u_begin;
-        const bool first = (c - c_row_lo) < NGROUP;   // the group's first tile of this row starts a new sum
-        const uint32_t v_addr = smem_u32(sm.v_tile[vb]), p_addr = smem_u32(sm.p_tile[grp]);
+        if (pi < qi && mbar_probe(smem_u32(&sm.p_ready[pi & 1]), (uint32_t)((pi >> 1) & 1)) &&
+            mbar_probe(smem_u32(&sm.v_full[pi % NBUF_V]), (uint32_t)((pi / NBUF_V) & 1))) {
+          const int c = pi, grp = c & 1, vb = c % NBUF_V;
+          tc_fence_after();
+          const int u = u_begin + c;
+          while (u >= sm.prefix[row_pv + 1]) ++row_pv;
+          const int c_row_lo = max(sm.prefix[row_pv], u_begin) - u_begin;
+          const bool first = (c - c_row_lo) < NGROUP;   // the group's first tile of this row starts a new sum
+          const uint32_t v_addr = smem_u32(sm.v_tile[vb]), p_addr = smem_u32(sm.p_tile[grp]);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          // A = XV^T: MN-major, 16 tokens per step (256 B), token groups of 8 are 128 B apart (LBO), latent
-          //     chunks 2048 B apart (SBO)
-          // B = P:    MN-major, token groups of 8 are 128 B apart (LBO); the second group of 8 columns aliases
-          //     the first (SBO 0): columns 8..15 of the result duplicate 0..7 and are never read
-          umma_f16(tmem_base + TM_O + 16 * grp, umma_desc(v_addr + ks * 256, 128, 2048),
-                   umma_desc(p_addr + ks * 256, 128, 0), idesc_o, (ks > 0 || !first) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks) {
+            // A = XV^T: MN-major, 16 tokens per step (256 B), token groups of 8 are 128 B apart (LBO), latent
+            //     chunks 2048 B apart (SBO)
+            // B = P:    MN-major, token groups of 8 are 128 B apart (LBO); the second group of 8 columns aliases
+            //     the first (SBO 0): columns 8..15 of the result duplicate 0..7 and are never read
+            umma_f16(tmem_base + TM_O + 16 * grp, umma_desc(v_addr + ks * 256, 128, 2048),
+                     umma_desc(p_addr + ks * 256, 128, 0), idesc_o, (ks > 0 || !first) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&sm.pv_done[grp]));
+          umma_commit(smem_u32(&sm.v_free[vb]));
+          ++pi;
+          progress = true;
         }
-        umma_commit(smem_u32(&sm.pv_done[grp]));
-        umma_commit(smem_u32(&sm.v_free[vb]));
+        if (progress) {
+          idle = 0;
+        } else {
+          ++idle;
+          if ((idle & 1023u) == 0u && *abort_flag) break;
+          if (idle >= SPIN_LIMIT) { *abort_flag = 1; break; }
+        }
       }
     }
   }

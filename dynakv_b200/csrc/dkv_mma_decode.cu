@@ -89,7 +89,7 @@ struct SmemLayout {
   int abort_flag;
   uint32_t tmem_base;
 };
-static_assert(sizeof(SmemLayout) + 1024 <= 227 * 1024, "shared memory budget");
+static_assert(sizeof(SmemLayout) <= 227 * 1024, "shared memory budget");
 static_assert(32 * 129 * 4 <= TILE_BYTES, "RoPE staging table must fit in one tile");
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -286,8 +286,10 @@ struct RowInfo { int row, arena, tokens, first_unit; };
 // ------------------------------------------------------------------ the kernel
 template <typename T, bool FUSED, bool KNORM>
 __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p, float log_theta, int n_cta) {
-  extern __shared__ unsigned char smem_raw[];
-  SmemLayout& sm = *reinterpret_cast<SmemLayout*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // The dynamic shared memory is used from its (aligned) start, so that every shared-memory address -- and with
+  // it every operand descriptor the tensor-core issuer builds -- is a link-time constant, not a run-time value.
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  SmemLayout& sm = *reinterpret_cast<SmemLayout*>(smem_raw);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = blockIdx.y;                        // KV head == basis group == arena within the batch row
@@ -1006,7 +1008,7 @@ __global__ void __launch_bounds__(128) split_combine_kernel(dkv_attn_args p) {
 }
 
 // ------------------------------------------------------------------ host side
-static size_t smem_bytes() { return sizeof(SmemLayout) + 1024; }
+static size_t smem_bytes() { return sizeof(SmemLayout); }
 
 bool mma_path_ok(const dkv_attn_args* a) {
   if (a->dtype != DKV_F16 && a->dtype != DKV_BF16) return false;

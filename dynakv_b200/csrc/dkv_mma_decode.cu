@@ -9,7 +9,7 @@
 // of the tile (tensor-memory lane = token), so neither RoPE nor the softmax needs a shuffle:
 //   2+2 gather warps : copy each token's ragged K / V coefficient row (16-byte cp.async, zero fill past the
 //                      row's length) into K-major, unswizzled 128 x 128 operand tiles in shared memory;
-//   1 MMA thread     : per tile  (1) K = X . Bk          M=128 tokens, N=128, K=128 (A, B from shared memory)
+//   2 MMA threads    : per tile  (1) K = X . Bk          M=128 tokens, N=128, K=128 (A, B from shared memory)
 //                                (2) S = K' . Q~^T       M=128 tokens, N=16,  K=128 (A = K' in tensor memory)
 //                                (3) O^T += XV^T . P     M=128 latent, N=16,  K=128 tokens (accumulates per row);
 //                      completion of each product is signalled by tcgen05.commit on mbarriers;
@@ -41,7 +41,8 @@ constexpr int W_MMA = 9;               // tcgen05.mma issuer, owns the tensor-me
 constexpr int W_KG0 = 10;              // K gather warps 10, 11 (64 tokens of the tile each)
 constexpr int W_VG0 = 12;              // V gather warps 12, 13
 constexpr int W_ROT2 = 14;             // second query rotator (quarters 2, 3 of each tile)
-constexpr int NTHREADS = 16 * 32;      // warp 15 is idle; 128 registers per thread
+constexpr int W_MMA2 = 15;             // second tcgen05.mma issuer: product (3)
+constexpr int NTHREADS = 16 * 32;      // 128 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
 constexpr int QSUB = 32;               // tokens per query-rotation quarter (= one token warp)
 constexpr int NBUF_A = 2;              // K operand tiles (= K accumulator buffers in tensor memory)
@@ -588,78 +589,55 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   }
 
   else if (warp == W_MMA) {
-    // =========================== tensor-core issuer ===========================
-    // One lane issues all three products.  It never blocks on one barrier: it probes, in turn, whether the next
-    // product (1), (2) or (3) has its operands in place and issues what is ready, so that waiting for one
-    // group's softmax does not hold back the other group's products.  The tensor core executes this thread's
-    // instructions in issue order, which also orders the re-use of the accumulator buffers: product (1) of tile
-    // i+2 is only issued after product (2) of tile i, which reads K' from the same buffer.
+    // =========================== tensor-core issuer A: products (1) and (2) ===========================
+    // One lane issues both products.  It never blocks on one barrier: it probes whether the next product (1) or
+    // (2) has its operands in place and issues what is ready, so that one group's RoPE pass does not hold back
+    // the other group's products.  The tensor core executes one thread's instructions in issue order, which also
+    // orders the re-use of the accumulator buffers: product (1) of tile i+2 is only issued after product (2) of
+    // tile i, which reads K' from the same buffer.  This thread is the serial part of the pipeline, so its code
+    // is kept short: fully unrolled issue loops over constant descriptors, probes issued back to back.
     if (lane == 0) {
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;   // 0 = f16, 1 = bf16
       const uint32_t idesc_k = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-      const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t basis_addr = smem_u32(sm.basis);
-      int ri = 0, qi = 0, pi = 0;     // next tile of products (1), (2), (3)
-      int row_pv = row0;
+      int ri = 0, qi = 0;     // next tile of products (1), (2)
       uint32_t idle = 0;
-      while (pi < n_stages) {
+      while (qi < n_stages) {
+        const int rb = ri & 1, qg = qi & 1;
+        const bool r_ok = mbar_probe(smem_u32(&sm.a_full[rb]), (uint32_t)((ri >> 1) & 1));
+        const bool k_ok = mbar_probe(smem_u32(&sm.kp_ready[qg]), (uint32_t)((qi >> 1) & 1));
+        const bool q_ok = mbar_probe(smem_u32(&sm.q_full[qg]), (uint32_t)((qi >> 1) & 1));
         bool progress = false;
-        if (ri < n_stages && ri - qi < NBUF_A && mbar_probe(smem_u32(&sm.a_full[ri % NBUF_A]), (uint32_t)((ri / NBUF_A) & 1))) {
-          const int buf = ri % NBUF_A;
+        if (ri < n_stages && ri - qi < NBUF_A && r_ok) {
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sm.a_tile[buf]);
+          const uint32_t a_addr = smem_u32(sm.a_tile[rb]);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             // A: K-major, 8-row core matrices 128 B apart (SBO), the two 8-coefficient chunks 2048 B apart (LBO)
             // B: MN-major, 8-column core matrices 128 B apart (SBO), the two 8-row groups 2048 B apart (LBO)
-            umma_f16(tmem_base + TM_K + buf * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
+            umma_f16(tmem_base + TM_K + rb * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
                      umma_desc(basis_addr + ks * 4096, 2048, 128), idesc_k, ks > 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&sm.t_ready[buf]));
-          umma_commit(smem_u32(&sm.a_free[buf]));
+          umma_commit(smem_u32(&sm.t_ready[rb]));
+          umma_commit(smem_u32(&sm.a_free[rb]));
           ++ri;
           progress = true;
         }
-        if (qi < ri && mbar_probe(smem_u32(&sm.kp_ready[qi & 1]), (uint32_t)((qi >> 1) & 1)) &&
-            mbar_probe(smem_u32(&sm.q_full[qi % NQ]), (uint32_t)((qi / NQ) & 1))) {
-          const int grp = qi & 1, slot = qi % NQ;
+        if (qi < ri && k_ok && q_ok && !(progress && qi + 1 == ri)) {
           tc_fence_after();
-          const uint32_t q_addr = smem_u32(sm.qrot[slot]);
-          const uint32_t kp = tmem_base + TM_K + grp * 128;
+          const uint32_t q_addr = smem_u32(sm.qrot[qg]);
+          const uint32_t kp = tmem_base + TM_K + qg * 128;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             // A: K' of the tile, dims 16ks..16ks+15 = packed columns 8ks.. (dims < 64) or 64 + 8(ks-4).. (dims >= 64)
             // B: K-major, head rows 16 B apart inside a core matrix, 8-row groups 128 B (SBO), dim chunks Q_LBO apart
-            umma_f16_ta(tmem_base + TM_S + 16 * grp, kp + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4)),
+            umma_f16_ta(tmem_base + TM_S + 16 * qg, kp + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4)),
                         umma_desc(q_addr + ks * 2 * Q_LBO, Q_LBO, 128), idesc_s, ks > 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&sm.s_ready[grp]));
-          umma_commit(smem_u32(&sm.q_free[slot]));
+          umma_commit(smem_u32(&sm.s_ready[qg]));
+          umma_commit(smem_u32(&sm.q_free[qg]));
           ++qi;
-          progress = true;
-        }
-        if (pi < qi && mbar_probe(smem_u32(&sm.p_ready[pi & 1]), (uint32_t)((pi >> 1) & 1)) &&
-            mbar_probe(smem_u32(&sm.v_full[pi % NBUF_V]), (uint32_t)((pi / NBUF_V) & 1))) {
-          const int c = pi, grp = c & 1, vb = c % NBUF_V;
-          tc_fence_after();
-          const int u = u_begin + c;
-          while (u >= sm.prefix[row_pv + 1]) ++row_pv;
-          const int c_row_lo = max(sm.prefix[row_pv], u_begin) - u_begin;
-          const bool first = (c - c_row_lo) < NGROUP;   // the group's first tile of this row starts a new sum
-          const uint32_t v_addr = smem_u32(sm.v_tile[vb]), p_addr = smem_u32(sm.p_tile[grp]);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            // A = XV^T: MN-major, 16 tokens per step (256 B), token groups of 8 are 128 B apart (LBO), latent
-            //     chunks 2048 B apart (SBO)
-            // B = P:    MN-major, token groups of 8 are 128 B apart (LBO); the second group of 8 columns aliases
-            //     the first (SBO 0): columns 8..15 of the result duplicate 0..7 and are never read
-            umma_f16(tmem_base + TM_O + 16 * grp, umma_desc(v_addr + ks * 256, 128, 2048),
-                     umma_desc(p_addr + ks * 256, 128, 0), idesc_o, (ks > 0 || !first) ? 1u : 0u);
-          }
-          umma_commit(smem_u32(&sm.pv_done[grp]));
-          umma_commit(smem_u32(&sm.v_free[vb]));
-          ++pi;
           progress = true;
         }
         if (progress) {
@@ -669,6 +647,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           if ((idle & 1023u) == 0u && *abort_flag) break;
           if (idle >= SPIN_LIMIT) { *abort_flag = 1; break; }
         }
+      }
+    }
+  }
+
+  else if (warp == W_MMA2) {
+    // =========================== tensor-core issuer B: product (3) ===========================
+    // A thread of its own (on another SM sub-partition), so that product (3) costs issuer A no time.
+    if (lane == 0) {
+      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+      int row_pv = row0;
+      int c_row_lo = 0, c_row_hi = 0;   // tiles of the current batch row in this CTA: [c_row_lo, c_row_hi)
+      for (int c = 0; c < n_stages; ++c) {
+        const int grp = c & 1, vb = c % NBUF_V;
+        if (c >= c_row_hi) {
+          const int u = u_begin + c;
+          while (u >= sm.prefix[row_pv + 1]) ++row_pv;
+          c_row_lo = max(sm.prefix[row_pv], u_begin) - u_begin;
+          c_row_hi = sm.prefix[row_pv + 1] - u_begin;
+        }
+        const bool first = (c - c_row_lo) < NGROUP;   // the group's first tile of this row starts a new sum
+        if (!mbar_wait_thread(smem_u32(&sm.v_full[vb]), (uint32_t)((c / NBUF_V) & 1), abort_flag)) break;
+        if (!mbar_wait_thread(smem_u32(&sm.p_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sm.v_tile[vb]), p_addr = smem_u32(sm.p_tile[grp]);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // A = XV^T: MN-major, 16 tokens per step (256 B), token groups of 8 are 128 B apart (LBO), latent
+          //     chunks 2048 B apart (SBO)
+          // B = P:    MN-major, token groups of 8 are 128 B apart (LBO); the second group of 8 columns aliases
+          //     the first (SBO 0): columns 8..15 of the result duplicate 0..7 and are never read
+          umma_f16(tmem_base + TM_O + 16 * grp, umma_desc(v_addr + ks * 256, 128, 2048),
+                   umma_desc(p_addr + ks * 256, 128, 0), idesc_o, (ks > 0 || !first) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sm.pv_done[grp]));
+        umma_commit(smem_u32(&sm.v_free[vb]));
       }
     }
   }
@@ -703,7 +717,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       tc_fence_after();
       // ---------------- K row from tensor memory: [RMSNorm,] RoPE, K' back as packed 16-bit pairs ----------------
       float ss = 0.f;
-#pragma unroll
+#pragma unroll 1   // kept rolled: the four warp roles of an SM sub-partition share a small instruction cache
       for (int i = 0; i < 8; ++i) {
         // pairs j = 8i..8i+7: dims j (columns 8i..) and j+64 (columns 64+8i..); table cells 16i..: per two pairs
         // {cos_j, cos_j+1, sin_j, sin_j+1}

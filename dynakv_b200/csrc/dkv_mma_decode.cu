@@ -13,8 +13,8 @@
 //                                (2) S = K' . Q~^T       M=128 tokens, N=16,  K=128 (A = K' in tensor memory)
 //                                (3) O^T += XV^T . P     M=128 latent, N=16,  K=128 tokens (accumulates per row);
 //                      completion of each product is signalled by tcgen05.commit on mbarriers;
-//   2 rotator warps  : Q~ = scale . R(-s) q for the four 32-token quarters of a tile (the B operand of (2)),
-//                      so token threads rotate K only by their local offset 0..31;
+//   1 rotator warp   : Q~ = scale . R(-s0) q for the tile's base position s0 (the B operand of (2)), so token
+//                      threads rotate K only by their in-tile offset 0..127;
 //   2 x 4 token warps: group g takes tiles of parity g.  A thread reads its token's K row from tensor memory
 //                      (tcgen05.ld.32x32b), applies [RMSNorm and] RoPE in fp32 with its 64 (cos, sin) pairs,
 //                      which also live in tensor memory (they depend on the lane only), and writes K' back as
@@ -40,11 +40,9 @@ constexpr int W_ROT = 8;               // query rotator
 constexpr int W_MMA = 9;               // tcgen05.mma issuer, owns the tensor-memory allocation
 constexpr int W_KG0 = 10;              // K gather warps 10, 11 (64 tokens of the tile each)
 constexpr int W_VG0 = 12;              // V gather warps 12, 13
-constexpr int W_ROT2 = 14;             // second query rotator (quarters 2, 3 of each tile)
 constexpr int W_MMA2 = 15;             // second tcgen05.mma issuer: product (3)
 constexpr int NTHREADS = 16 * 32;      // 128 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
-constexpr int QSUB = 32;               // tokens per query-rotation quarter (= one token warp)
 constexpr int NBUF_A = 2;              // K operand tiles (= K accumulator buffers in tensor memory)
 constexpr int NBUF_V = 3;              // V operand tiles
 constexpr int NQ = 2;                  // rotated-query tiles
@@ -91,7 +89,7 @@ struct SmemLayout {
   uint32_t tmem_base;
 };
 static_assert(sizeof(SmemLayout) <= 227 * 1024, "shared memory budget");
-static_assert(32 * 129 * 4 <= TILE_BYTES, "RoPE staging table must fit in one tile");
+static_assert(ST_TOK * 129 * 4 <= NBUF_V * TILE_BYTES, "RoPE staging table must fit in the V tiles");
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -318,7 +316,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       sm.abort_flag = 0;
       for (int s = 0; s < NBUF_A; ++s) { mbar_init(smem_u32(&sm.a_full[s]), 2); mbar_init(smem_u32(&sm.a_free[s]), 1); }
       for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 2); mbar_init(smem_u32(&sm.v_free[s]), 1); }
-      for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 2); mbar_init(smem_u32(&sm.q_free[s]), 1); }
+      for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 1); mbar_init(smem_u32(&sm.q_free[s]), 1); }
       for (int s = 0; s < NGROUP; ++s) {
         mbar_init(smem_u32(&sm.t_ready[s]), 1);
         mbar_init(smem_u32(&sm.kp_ready[s]), 4);
@@ -376,18 +374,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
                    "r"(TMEM_COLS));
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
-    // RoPE table for local offsets t = 0..31: angle = t * f_j, f_j = exp(-(2j/D) ln theta), staged as
+    // RoPE table for the in-tile offsets t = 0..127: angle = t * f_j, f_j = exp(-(2j/D) ln theta), staged as
     // tr[t][4*(j/2) + (j&1)] = cos, [.. + 2] = sin (row pitch 129 floats).  NTHREADS is a multiple of 64, so a
     // thread keeps one j and steps t by NTHREADS/64: one exact sincos, then a fixed-angle rotation per step.
     static_assert(NTHREADS % 64 == 0, "trig table fill assumes a fixed j per thread");
     constexpr int TSTEP = NTHREADS / 64;
-    float* tr = reinterpret_cast<float*>(sm.v_tile[NBUF_V - 1]);
+    float* tr = reinterpret_cast<float*>(sm.v_tile[0]);   // spans the (contiguous) V tiles until the pipeline starts
     const int j = tid & 63;
     const float f = expf(-((float)(2 * j) / (float)D) * log_theta);
     float sn, cs, ds, dc;
     sincosf((float)(tid >> 6) * f, &sn, &cs);
     sincosf((float)TSTEP * f, &ds, &dc);
-    for (int t = tid >> 6; t < QSUB; t += TSTEP) {
+    for (int t = tid >> 6; t < ST_TOK; t += TSTEP) {
       const int idx = t * 129 + 4 * (j >> 1) + (j & 1);
       tr[idx] = cs;
       tr[idx + 2] = sn;
@@ -395,6 +393,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       cs = c2; sn = s2;
     }
     if (KNORM && tid < D) sm.knorm_w[tid] = p.k_norm_weight[tid];
+    for (int e = tid; e < NQ * Q_TILE_BYTES / 4; e += NTHREADS) reinterpret_cast<uint32_t*>(sm.qrot)[e] = 0u;   // rows the rotator never writes
   }
   tc_fence_before();
   __syncthreads();
@@ -402,7 +401,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   const uint32_t tmem_base = sm.tmem_base;
   if (warp < 4) {
     // the table row of this thread's local offset goes to its tensor-memory lane (both groups read it there)
-    const float* tr = reinterpret_cast<const float*>(sm.v_tile[NBUF_V - 1]) + lane * 129;
+    const float* tr = reinterpret_cast<const float*>(sm.v_tile[0]) + tid * 129;
     const uint32_t dst = tmem_base + ((uint32_t)(32 * warp) << 16) + TM_TRIG;
 #pragma unroll
     for (int blk = 0; blk < 8; ++blk) {
@@ -436,20 +435,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     ri.first_unit = sm.prefix[ri.row];
   };
 
-  if (warp == W_ROT || warp == W_ROT2) {
+  if (warp == W_ROT) {
     // =========================== query rotator warp ===========================
-    // For the four 32-token quarters of every tile (base position s) the two rotator warps (quarters 0,1 and
-    // 2,3) publish Q~ = scale * R(-s) q for the group's heads as row n = 4*quarter + head of the B operand of
-    // product (2), so that q~ . R(t) k = q . R(s + t) k with the local offset t = 0..31.  Lane l owns the pairs
-    // j = 2l, 2l+1.
+    // For every tile (base position s0) it publishes Q~ = scale * R(-s0) q for the group's heads as rows 0..3 of
+    // the B operand of product (2), so that q~ . R(t) k = q . R(s0 + t) k with the in-tile offset t = 0..127
+    // (the rotation the token threads apply).  Rows 4..15 stay zero.  Lane l owns the pairs j = 2l, 2l+1.
     const float f0 = expf(-((float)(4 * lane) / (float)D) * log_theta);
     const float f1 = expf(-((float)(4 * lane + 2) / (float)D) * log_theta);
-    const int qt0 = (warp == W_ROT) ? 0 : 2;          // this warp's first quarter
-    float cd0, sd0, cd1, sd1, ct0, st0, ct1, st1;     // rotation by one quarter / by the three quarters to the next tile
-    sincosf((float)QSUB * f0, &sd0, &cd0);
-    sincosf((float)QSUB * f1, &sd1, &cd1);
-    sincosf((float)(ST_TOK - QSUB) * f0, &st0, &ct0);
-    sincosf((float)(ST_TOK - QSUB) * f1, &st1, &ct1);
+    float cd0, sd0, cd1, sd1;     // rotation by one tile
+    sincosf((float)ST_TOK * f0, &sd0, &cd0);
+    sincosf((float)ST_TOK * f1, &sd1, &cd1);
     const float qscale = rsqrtf((float)D) * 1.4426950408889634f;  // softmax scale and log2(e) folded into q
     float a0[HP], b0[HP], a1[HP], b1[HP];   // (q~_j, q~_{j+64}) for j = 2l and j = 2l+1
     int row = row0;
@@ -459,44 +454,36 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const int u = u_begin + c;
       while (u >= sm.prefix[row + 1]) ++row;
       const bool row_start = (c == 0) || (u == sm.prefix[row]);
-      const int b = p.batch_index ? p.batch_index[row] : row;
-      const int s0 = (u - sm.prefix[row]) * ST_TOK;
-      unsigned char* const qt_base = sm.qrot[slot] + (lane >> 2) * Q_LBO + (lane & 3) * 4;
-#pragma unroll
-      for (int qq = 0; qq < 2; ++qq) {
-        const int qt = qt0 + qq;
-        if (row_start && qq == 0) {
-          float sa, ca, sb, cb;
-          sincosf((float)(s0 + qt0 * QSUB) * f0, &sa, &ca);
-          sincosf((float)(s0 + qt0 * QSUB) * f1, &sb, &cb);
-#pragma unroll
-          for (int h = 0; h < HP; ++h) {
-            float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
-            if (h < G) {
-              const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)(g * G + h) * p.q_stride_h;
-              x0 = to_f32(qp[2 * lane]) * qscale; x1 = to_f32(qp[2 * lane + 64]) * qscale;
-              y0 = to_f32(qp[2 * lane + 1]) * qscale; y1 = to_f32(qp[2 * lane + 65]) * qscale;
-            }
-            a0[h] = x0 * ca + x1 * sa; b0[h] = x1 * ca - x0 * sa;
-            a1[h] = y0 * cb + y1 * sb; b1[h] = y1 * cb - y0 * sb;
-          }
-        } else {
-          // from this warp's previous quarter: one quarter on (qq == 1) or three quarters on (next tile)
-          const float c0 = qq ? cd0 : ct0, s0r = qq ? sd0 : st0, c1 = qq ? cd1 : ct1, s1r = qq ? sd1 : st1;
-#pragma unroll
-          for (int h = 0; h < HP; ++h) {
-            const float x0 = a0[h], x1 = b0[h], y0 = a1[h], y1 = b1[h];
-            a0[h] = x0 * c0 + x1 * s0r; b0[h] = x1 * c0 - x0 * s0r;
-            a1[h] = y0 * c1 + y1 * s1r; b1[h] = y1 * c1 - y0 * s1r;
-          }
-        }
+      if (row_start) {
+        const int b = p.batch_index ? p.batch_index[row] : row;
+        const int s0 = (u - sm.prefix[row]) * ST_TOK;
+        float sa, ca, sb, cb;
+        sincosf((float)s0 * f0, &sa, &ca);
+        sincosf((float)s0 * f1, &sb, &cb);
 #pragma unroll
         for (int h = 0; h < HP; ++h) {
-          const int n = qt * HP + h;
-          unsigned char* w = qt_base + (n >> 3) * 128 + (n & 7) * 16;
-          *reinterpret_cast<uint32_t*>(w) = Pack<T>::two(a0[h], a1[h]);                 // dims 2l, 2l+1
-          *reinterpret_cast<uint32_t*>(w + 8 * Q_LBO) = Pack<T>::two(b0[h], b1[h]);     // dims 2l+64, 2l+65
+          float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
+          if (h < G) {
+            const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)(g * G + h) * p.q_stride_h;
+            x0 = to_f32(qp[2 * lane]) * qscale; x1 = to_f32(qp[2 * lane + 64]) * qscale;
+            y0 = to_f32(qp[2 * lane + 1]) * qscale; y1 = to_f32(qp[2 * lane + 65]) * qscale;
+          }
+          a0[h] = x0 * ca + x1 * sa; b0[h] = x1 * ca - x0 * sa;
+          a1[h] = y0 * cb + y1 * sb; b1[h] = y1 * cb - y0 * sb;
         }
+      } else {
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          const float x0 = a0[h], x1 = b0[h], y0 = a1[h], y1 = b1[h];
+          a0[h] = x0 * cd0 + x1 * sd0; b0[h] = x1 * cd0 - x0 * sd0;
+          a1[h] = y0 * cd1 + y1 * sd1; b1[h] = y1 * cd1 - y0 * sd1;
+        }
+      }
+      unsigned char* const w0 = sm.qrot[slot] + (lane >> 2) * Q_LBO + (lane & 3) * 4;
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        *reinterpret_cast<uint32_t*>(w0 + h * 16) = Pack<T>::two(a0[h], a1[h]);                 // dims 2l, 2l+1
+        *reinterpret_cast<uint32_t*>(w0 + h * 16 + 8 * Q_LBO) = Pack<T>::two(b0[h], b1[h]);     // dims 2l+64, 2l+65
       }
       proxy_fence_async();
       __syncwarp();
@@ -695,7 +682,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   const int tok = 32 * wq + lane;
   const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * wq) << 16);
   const uint32_t k_addr = lane_addr + TM_K + 128 * grp;
-  const uint32_t s_addr = lane_addr + TM_S + 16 * grp + 4 * wq;   // this quarter's columns: n = 4 wq + head
+  const uint32_t s_addr = lane_addr + TM_S + 16 * grp;   // columns = heads
   const uint32_t o_addr = lane_addr + TM_O + 16 * grp;
 
   int row = row0;

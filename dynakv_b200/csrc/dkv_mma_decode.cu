@@ -158,6 +158,10 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+// The barrier receives one arrival from this thread once all of its earlier cp.async copies have landed.
+__device__ __forceinline__ void cp_async_arrive_when_landed(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -314,8 +318,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     if (lane == 0) {
       sm.prefix[0] = 0;
       sm.abort_flag = 0;
-      for (int s = 0; s < NBUF_A; ++s) { mbar_init(smem_u32(&sm.a_full[s]), 2); mbar_init(smem_u32(&sm.a_free[s]), 1); }
-      for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 2); mbar_init(smem_u32(&sm.v_free[s]), 1); }
+      for (int s = 0; s < NBUF_A; ++s) { mbar_init(smem_u32(&sm.a_full[s]), 64); mbar_init(smem_u32(&sm.a_free[s]), 1); }
+      for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 64); mbar_init(smem_u32(&sm.v_free[s]), 1); }
       for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 1); mbar_init(smem_u32(&sm.q_free[s]), 1); }
       for (int s = 0; s < NGROUP; ++s) {
         mbar_init(smem_u32(&sm.t_ready[s]), 1);
@@ -524,12 +528,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       }
     };
     for (int c = 0; c < PD; ++c) { prefetch_meta(c); cp_async_commit(); }   // groups 0..PD-1
-    auto publish = [&](int c) {   // the copies of tile c have landed: hand the tile over
-      proxy_fence_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(is_v ? &sm.v_full[c % NBUF_V] : &sm.a_full[c % NBUF_A]));
-    };
-    bool ok = true;
     for (int c = 0; c < n_stages; ++c) {
       const int buf = c % NB;
       cp_async_wait<PD - 1>();   // group c (this tile's metadata) is complete
@@ -551,10 +549,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         if (lane == 0) { sm.kvalid[c % KV_RING][2 * gw] = m0; sm.kvalid[c % KV_RING][2 * gw + 1] = m1; }
       }
       // the tensor core must be done with the tile that was in this buffer NB tiles ago
-      if (c >= NB && !mbar_wait(smem_u32(is_v ? &sm.v_free[buf] : &sm.a_free[buf]), (uint32_t)(((c / NB) - 1) & 1), abort_flag)) {
-        ok = false;
-        break;
-      }
+      if (c >= NB && !mbar_wait(smem_u32(is_v ? &sm.v_free[buf] : &sm.a_free[buf]), (uint32_t)(((c / NB) - 1) & 1), abort_flag)) break;
       unsigned char* const tile = is_v ? sm.v_tile[buf] : sm.a_tile[buf];
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
@@ -567,12 +562,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           cp_async16_zfill(dst + ch * 2048, in ? row_src + ch * 16 : row_src, in ? 16 : 0);
         }
       }
+      // The tile is handed over by the copy engine itself: each lane's arrival on the tile's barrier fires when
+      // its copies have landed, so the warp neither waits for the data nor delays the hand-over until it comes
+      // round again (which would put the next tile's wait for a free buffer into the serial loop
+      // buffer free -> copies -> product (1) -> buffer free).  The consumer issues the proxy fence.
+      cp_async_arrive_when_landed(smem_u32(is_v ? &sm.v_full[buf] : &sm.a_full[buf]));
       prefetch_meta(c + PD);
       cp_async_commit();                       // group PD + c
-      if (c >= 1) { cp_async_wait<1>(); publish(c - 1); }   // groups up to PD + c - 1 are complete
     }
     cp_async_wait<0>();
-    if (ok) publish(n_stages - 1);
   }
 
   else if (warp == W_MMA) {
@@ -597,6 +595,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         const bool q_ok = mbar_probe(smem_u32(&sm.q_full[qg]), (uint32_t)((qi >> 1) & 1));
         bool progress = false;
         if (ri < n_stages && ri - qi < NBUF_A && r_ok) {
+          proxy_fence_async();   // the tile was written by cp.async (generic proxy), the tensor core reads it through the async proxy
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sm.a_tile[rb]);
 #pragma unroll
@@ -657,6 +656,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         const bool first = (c - c_row_lo) < NGROUP;   // the group's first tile of this row starts a new sum
         if (!mbar_wait_thread(smem_u32(&sm.v_full[vb]), (uint32_t)((c / NBUF_V) & 1), abort_flag)) break;
         if (!mbar_wait_thread(smem_u32(&sm.p_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
+        proxy_fence_async();   // V tile written by cp.async
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sm.v_tile[vb]), p_addr = smem_u32(sm.p_tile[grp]);
 #pragma unroll

@@ -36,11 +36,14 @@ namespace dkv {
 constexpr int D = 128;
 constexpr int NGROUP = 2;              // token-thread groups: warps 0-3 (even tiles), 4-7 (odd tiles)
 constexpr int NCW = 4 * NGROUP;        // token warps
-constexpr int W_ROT = 8;               // query rotator
-constexpr int W_MMA = 9;               // tcgen05.mma issuer, owns the tensor-memory allocation
-constexpr int W_KG0 = 10;              // K gather warps 10, 11 (64 tokens of the tile each)
-constexpr int W_VG0 = 12;              // V gather warps 12, 13
-constexpr int W_MMA2 = 15;             // second tcgen05.mma issuer: product (3)
+// Service warps.  Warp w runs on SM sub-partition w % 4, next to token warps w % 4 and 4 + w % 4; the roles are
+// placed so that the sub-partitions of the two issuer threads do not also hold the (large) gather code: the
+// instruction caches are small and the issuers' instruction stream is the serial part of the pipeline.
+constexpr int W_KG0 = 8;               // K gather warps 8, 12 (64 tokens of the tile each)
+constexpr int W_VG0 = 9;               // V gather warps 9, 13
+constexpr int W_MMA = 10;              // tcgen05.mma issuer for products (1), (2); owns the tensor-memory allocation
+constexpr int W_ROT = 14;              // query rotator
+constexpr int W_MMA2 = 11;             // tcgen05.mma issuer for product (3)
 constexpr int NTHREADS = 16 * 32;      // 128 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
 constexpr int NBUF_A = 2;              // K operand tiles (= K accumulator buffers in tensor memory)
@@ -495,14 +498,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
   }
 
-  else if (warp >= W_KG0 && warp < W_KG0 + 4) {
+  else if (warp == W_KG0 || warp == W_KG0 + 4 || warp == W_VG0 || warp == W_VG0 + 4) {
     // =========================== gather warps ===========================
     // Lane l of gather warp j (of its side) owns tokens 64j + l and 64j + 32 + l of every tile: it stages their
     // lengths and offsets (cp.async, PD tiles ahead, slots private to the lane) and copies each coefficient row
     // into the operand tile, one 16-byte chunk per cp.async, chunk c of token t at c*2048 + t*16; chunks past
     // the row's length are zero-filled (source size 0), so the tensor core always sees a full 128 x 128 tile.
-    const bool is_v = warp >= W_VG0;
-    const int gw = (warp - W_KG0) & 1;
+    const bool is_v = (warp & 3) == (W_VG0 & 3);
+    const int gw = (warp >> 2) & 1;
     const dkv_side& sd = is_v ? p.v : p.k;
     const int side = is_v ? 1 : 0;
     const int NB = is_v ? NBUF_V : NBUF_A;

@@ -46,7 +46,8 @@ constexpr int W_ROT = 14;              // query rotator
 constexpr int W_MMA2 = 11;             // tcgen05.mma issuer for product (3)
 constexpr int NTHREADS = 16 * 32;      // 128 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
-constexpr int NBUF_A = 2;              // K operand tiles (= K accumulator buffers in tensor memory)
+constexpr int NBUF_A = 2;              // K operand tiles in shared memory
+constexpr int NBUF_T = 3;              // K accumulator buffers in tensor memory (held from product (1) to product (2))
 constexpr int NBUF_V = 3;              // V operand tiles
 constexpr int NQ = 2;                  // rotated-query tiles
 constexpr int PD = 2;                  // prefetch distance of the gather warps' metadata (tiles)
@@ -60,8 +61,9 @@ constexpr int MAX_BATCH = 1024;
 constexpr int PART_STRIDE = 2 + 128;   // floats per (head) partial record: m, l, latent[128]
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr float M_SLACK = 8.f;         // a tile may exceed the reference maximum by 2^8 before O is rescaled
-// tensor-memory columns (fp32 cells): two K accumulators, the RoPE table, two score tiles, two O accumulators
-constexpr uint32_t TM_K = 0, TM_TRIG = 256, TM_S = 384, TM_O = 416, TMEM_COLS = 512;
+// tensor-memory columns (32-bit cells): three K accumulators, the RoPE table (fp16 pairs), two score tiles, one O
+// accumulator
+constexpr uint32_t TM_K = 0, TM_TRIG = 384, TM_S = 448, TM_O = 480, TMEM_COLS = 512;
 
 struct SmemLayout {
   alignas(1024) unsigned char a_tile[NBUF_A][TILE_BYTES];   // chunk c (8 coefficients) of token t at c*2048 + t*16
@@ -70,9 +72,10 @@ struct SmemLayout {
   alignas(128) unsigned char qrot[NQ][Q_TILE_BYTES];        // Q~[n][d] at (d/8)*272 + (n/8)*128 + (n%8)*16 + (d%8)*2
   alignas(128) unsigned char p_tile[NGROUP][ST_TOK * 16];   // P[t][n < 8] at t*16
   alignas(16) int meta[2][MSLOT][2][ST_TOK];                // [K|V][slot][lens|offs][token]
-  alignas(16) float merge[NGROUP][HP][PART_STRIDE];
-  alignas(16) float tmax[NGROUP][2][4][4];                  // [group][tile parity][warp][head]
-  alignas(16) float lsum[NGROUP][4][4];                     // [group][warp][head]
+  alignas(16) float lat[HP][128];                           // fused path: normalised latent result of a row
+  alignas(16) float tmax[2][4][4];                          // [tile parity][warp][head]
+  alignas(16) float lsum[4][4];                             // [warp][head]
+  alignas(16) float rs_buf[4][ST_TOK];                      // K-RMSNorm: 1/rms of the tokens of the last four tiles
   alignas(16) float knorm_w[D];
   uint32_t kvalid[KV_RING][4];                              // bit l of word w: token 32w + l of the tile has a K row
   alignas(8) unsigned long long a_full[NBUF_A];    // K operand tile written (2 gather warps)
@@ -81,18 +84,18 @@ struct SmemLayout {
   alignas(8) unsigned long long v_free[NBUF_V];    // product (3) done with it (commit)
   alignas(8) unsigned long long q_full[NQ];        // rotated queries written (rotator)
   alignas(8) unsigned long long q_free[NQ];        // product (2) done with them (commit)
-  alignas(8) unsigned long long t_ready[NGROUP];   // K accumulator written (commit)
-  alignas(8) unsigned long long kp_ready[NGROUP];  // K' written back to tensor memory (4 token warps)
+  alignas(8) unsigned long long t_ready[NBUF_T];   // K accumulator written (commit)
+  alignas(8) unsigned long long kp_ready[NBUF_T];  // K' written back to tensor memory (4 RoPE warps)
   alignas(8) unsigned long long s_ready[NGROUP];   // scores written (commit)
   alignas(8) unsigned long long p_ready[NGROUP];   // P tile written (4 token warps)
   alignas(8) unsigned long long pv_done[NGROUP];   // product (3) done: O updated, P tile free (commit)
-  alignas(8) unsigned long long grp_sync[NGROUP];  // per-tile rendezvous of a group's 4 warps (tile maxima)
+  alignas(8) unsigned long long grp_sync;          // per-tile rendezvous of the 4 softmax warps (tile maxima)
   int prefix[MAX_BATCH + 1];
   int abort_flag;
   uint32_t tmem_base;
 };
 static_assert(sizeof(SmemLayout) <= 227 * 1024, "shared memory budget");
-static_assert(ST_TOK * 129 * 4 <= NBUF_V * TILE_BYTES, "RoPE staging table must fit in the V tiles");
+static_assert(ST_TOK * 65 * 4 <= NBUF_V * TILE_BYTES, "RoPE staging table must fit in the V tiles");
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -197,25 +200,22 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // Thread-per-lane tensor-memory access (32x32b shapes): thread i of the warp addresses lane (base lane + i),
 // register k holds column (base column + k).  Every load carries its wait in the same statement, so no
 // result register can be touched before the data has landed.
-// One RoPE chunk: 8 K values of dims j0..j0+7, their rotation partners (dims +64) and the 16 table cells.
-__device__ __forceinline__ void tmem_ld_rope_chunk(float (&lo)[8], float (&hi)[8], float (&tg)[16], uint32_t a_lo,
+// One RoPE chunk: 8 K values of dims j0..j0+7, their rotation partners (dims +64) and the 8 table cells (fp16 pairs).
+__device__ __forceinline__ void tmem_ld_rope_chunk(float (&lo)[8], float (&hi)[8], uint32_t (&tg)[8], uint32_t a_lo,
                                                    uint32_t a_hi, uint32_t a_tg) {
-  uint32_t r[32];
+  uint32_t r[16];
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%32];\n"
-      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%8,%9,%10,%11,%12,%13,%14,%15}, [%33];\n"
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%34];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%24];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%8,%9,%10,%11,%12,%13,%14,%15}, [%25];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%16,%17,%18,%19,%20,%21,%22,%23}, [%26];\n"
       "tcgen05.wait::ld.sync.aligned;"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "=r"(tg[0]), "=r"(tg[1]), "=r"(tg[2]), "=r"(tg[3]), "=r"(tg[4]), "=r"(tg[5]), "=r"(tg[6]), "=r"(tg[7])
       : "r"(a_lo), "r"(a_hi), "r"(a_tg)
       : "memory");
 #pragma unroll
   for (int i = 0; i < 8; ++i) { lo[i] = __uint_as_float(r[i]); hi[i] = __uint_as_float(r[8 + i]); }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) tg[i] = __uint_as_float(r[16 + i]);
 }
 __device__ __forceinline__ void tmem_ld4(float (&v)[4], uint32_t addr) {
   uint32_t r[4];
@@ -240,7 +240,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t addr, const float (&v)[16]) {
                : "memory");
 }
 
-__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(4 * 32) : "memory"); }   // the 4 softmax warps
 
 // order-preserving map float -> int (and back: the map is its own inverse), for redux.sync
 __device__ __forceinline__ int float_key(float f) {
@@ -325,13 +325,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 64); mbar_init(smem_u32(&sm.v_free[s]), 1); }
       for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 1); mbar_init(smem_u32(&sm.q_free[s]), 1); }
       for (int s = 0; s < NGROUP; ++s) {
-        mbar_init(smem_u32(&sm.t_ready[s]), 1);
-        mbar_init(smem_u32(&sm.kp_ready[s]), 4);
         mbar_init(smem_u32(&sm.s_ready[s]), 1);
         mbar_init(smem_u32(&sm.p_ready[s]), 4);
         mbar_init(smem_u32(&sm.pv_done[s]), 1);
-        mbar_init(smem_u32(&sm.grp_sync[s]), 4);
       }
+      for (int s = 0; s < NBUF_T; ++s) { mbar_init(smem_u32(&sm.t_ready[s]), 1); mbar_init(smem_u32(&sm.kp_ready[s]), 4); }
+      mbar_init(smem_u32(&sm.grp_sync), 4);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
   }
@@ -382,20 +381,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
     // RoPE table for the in-tile offsets t = 0..127: angle = t * f_j, f_j = exp(-(2j/D) ln theta), staged as
-    // tr[t][4*(j/2) + (j&1)] = cos, [.. + 2] = sin (row pitch 129 floats).  NTHREADS is a multiple of 64, so a
+    // 16-bit cells tr[t][4*(j/2) + (j&1)] = cos, [.. + 2] = sin (row pitch 130 cells = 65 words): per two pairs one
+    // word of cosines and one of sines, kept in fp16 (2^-11 absolute, below the 16-bit rounding of K').  NTHREADS is a multiple of 64, so a
     // thread keeps one j and steps t by NTHREADS/64: one exact sincos, then a fixed-angle rotation per step.
     static_assert(NTHREADS % 64 == 0, "trig table fill assumes a fixed j per thread");
     constexpr int TSTEP = NTHREADS / 64;
-    float* tr = reinterpret_cast<float*>(sm.v_tile[0]);   // spans the (contiguous) V tiles until the pipeline starts
+    __half* tr = reinterpret_cast<__half*>(sm.v_tile[0]);   // spans the (contiguous) V tiles until the pipeline starts
     const int j = tid & 63;
     const float f = expf(-((float)(2 * j) / (float)D) * log_theta);
     float sn, cs, ds, dc;
     sincosf((float)(tid >> 6) * f, &sn, &cs);
     sincosf((float)TSTEP * f, &ds, &dc);
     for (int t = tid >> 6; t < ST_TOK; t += TSTEP) {
-      const int idx = t * 129 + 4 * (j >> 1) + (j & 1);
-      tr[idx] = cs;
-      tr[idx + 2] = sn;
+      const int idx = t * 130 + 4 * (j >> 1) + (j & 1);
+      tr[idx] = __float2half_rn(cs);
+      tr[idx + 2] = __float2half_rn(sn);
       const float c2 = cs * dc - sn * ds, s2 = sn * dc + cs * ds;
       cs = c2; sn = s2;
     }
@@ -408,10 +408,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   const uint32_t tmem_base = sm.tmem_base;
   if (warp < 4) {
     // the table row of this thread's local offset goes to its tensor-memory lane (both groups read it there)
-    const float* tr = reinterpret_cast<const float*>(sm.v_tile[0]) + tid * 129;
+    const float* tr = reinterpret_cast<const float*>(sm.v_tile[0]) + tid * 65;   // 64 packed words of this row
     const uint32_t dst = tmem_base + ((uint32_t)(32 * warp) << 16) + TM_TRIG;
 #pragma unroll
-    for (int blk = 0; blk < 8; ++blk) {
+    for (int blk = 0; blk < 4; ++blk) {
       float v[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) v[i] = tr[16 * blk + i];
@@ -581,7 +581,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     // One lane issues both products.  It never blocks on one barrier: it probes whether the next product (1) or
     // (2) has its operands in place and issues what is ready, so that one group's RoPE pass does not hold back
     // the other group's products.  The tensor core executes one thread's instructions in issue order, which also
-    // orders the re-use of the accumulator buffers: product (1) of tile i+2 is only issued after product (2) of
+    // orders the re-use of the accumulator buffers: product (1) of tile i+3 is only issued after product (2) of
     // tile i, which reads K' from the same buffer.  This thread is the serial part of the pipeline, so its code
     // is kept short: fully unrolled issue loops over constant descriptors, probes issued back to back.
     if (lane == 0) {
@@ -590,14 +590,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t basis_addr = smem_u32(sm.basis);
       int ri = 0, qi = 0;     // next tile of products (1), (2)
+      int rt = 0, qt = 0;     // their accumulator buffers ri % 3, qi % 3 ...
+      uint32_t rtp = 0, qtp = 0;   // ... and phases (ri / 3) & 1, (qi / 3) & 1
       uint32_t idle = 0;
       while (qi < n_stages) {
         const int rb = ri & 1, qg = qi & 1;
         const bool r_ok = mbar_probe(smem_u32(&sm.a_full[rb]), (uint32_t)((ri >> 1) & 1));
-        const bool k_ok = mbar_probe(smem_u32(&sm.kp_ready[qg]), (uint32_t)((qi >> 1) & 1));
-        const bool q_ok = mbar_probe(smem_u32(&sm.q_full[qg]), (uint32_t)((qi >> 1) & 1));
+        const bool k_ok = mbar_probe(smem_u32(&sm.kp_ready[qt]), qtp);
+        const bool q_ok = mbar_probe(smem_u32(&sm.q_full[qg]), (uint32_t)((qi >> 1) & 1)) &&
+                          (qi < 2 || mbar_probe(smem_u32(&sm.p_ready[qg]), (uint32_t)(((qi >> 1) - 1) & 1)));   // score tile read out
         bool progress = false;
-        if (ri < n_stages && ri - qi < NBUF_A && r_ok) {
+        if (ri < n_stages && ri - qi < NBUF_T && r_ok) {
           proxy_fence_async();   // the tile was written by cp.async (generic proxy), the tensor core reads it through the async proxy
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sm.a_tile[rb]);
@@ -605,18 +608,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           for (int ks = 0; ks < 8; ++ks) {
             // A: K-major, 8-row core matrices 128 B apart (SBO), the two 8-coefficient chunks 2048 B apart (LBO)
             // B: MN-major, 8-column core matrices 128 B apart (SBO), the two 8-row groups 2048 B apart (LBO)
-            umma_f16(tmem_base + TM_K + rb * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
+            umma_f16(tmem_base + TM_K + rt * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
                      umma_desc(basis_addr + ks * 4096, 2048, 128), idesc_k, ks > 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&sm.t_ready[rb]));
+          umma_commit(smem_u32(&sm.t_ready[rt]));
           umma_commit(smem_u32(&sm.a_free[rb]));
           ++ri;
+          if (++rt == NBUF_T) { rt = 0; rtp ^= 1u; }
           progress = true;
         }
         if (qi < ri && k_ok && q_ok && !(progress && qi + 1 == ri)) {
           tc_fence_after();
           const uint32_t q_addr = smem_u32(sm.qrot[qg]);
-          const uint32_t kp = tmem_base + TM_K + qg * 128;
+          const uint32_t kp = tmem_base + TM_K + qt * 128;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             // A: K' of the tile, dims 16ks..16ks+15 = packed columns 8ks.. (dims < 64) or 64 + 8(ks-4).. (dims >= 64)
@@ -627,6 +631,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           umma_commit(smem_u32(&sm.s_ready[qg]));
           umma_commit(smem_u32(&sm.q_free[qg]));
           ++qi;
+          if (++qt == NBUF_T) { qt = 0; qtp ^= 1u; }
           progress = true;
         }
         if (progress) {
@@ -656,7 +661,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           c_row_lo = max(sm.prefix[row_pv], u_begin) - u_begin;
           c_row_hi = sm.prefix[row_pv + 1] - u_begin;
         }
-        const bool first = (c - c_row_lo) < NGROUP;   // the group's first tile of this row starts a new sum
+        const bool first = c == c_row_lo;   // the first tile of a row starts a new sum
         if (!mbar_wait_thread(smem_u32(&sm.v_full[vb]), (uint32_t)((c / NBUF_V) & 1), abort_flag)) break;
         if (!mbar_wait_thread(smem_u32(&sm.p_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
         proxy_fence_async();   // V tile written by cp.async
@@ -668,7 +673,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           //     chunks 2048 B apart (SBO)
           // B = P:    MN-major, token groups of 8 are 128 B apart (LBO); the second group of 8 columns aliases
           //     the first (SBO 0): columns 8..15 of the result duplicate 0..7 and are never read
-          umma_f16(tmem_base + TM_O + 16 * grp, umma_desc(v_addr + ks * 256, 128, 2048),
+          umma_f16(tmem_base + TM_O, umma_desc(v_addr + ks * 256, 128, 2048),
                    umma_desc(p_addr + ks * 256, 128, 0), idesc_o, (ks > 0 || !first) ? 1u : 0u);
         }
         umma_commit(smem_u32(&sm.pv_done[grp]));
@@ -677,42 +682,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
   }
 
-  else if (warp < NCW) {
-  // ============================= token warps =============================
-  // Group grp = warp / 4 takes the tiles of parity grp.  Thread (wq, lane) owns token 32 wq + lane of each of
-  // them, which is tensor-memory lane 32 wq + lane -- the lanes a warp in SM sub-partition wq may access.
-  const int grp = warp >> 2, wq = warp & 3;
-  const int tok = 32 * wq + lane;
-  const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * wq) << 16);
-  const uint32_t k_addr = lane_addr + TM_K + 128 * grp;
-  const uint32_t s_addr = lane_addr + TM_S + 16 * grp;   // columns = heads
-  const uint32_t o_addr = lane_addr + TM_O + 16 * grp;
-
-  int row = row0;
-  while (row < p.batch && sm.prefix[row] < u_end) {
-    const int c_lo = max(sm.prefix[row], u_begin) - u_begin;     // tiles of this row in this CTA: [c_lo, c_hi)
-    const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;
-    float m_ref[HP], l_part[HP];
-#pragma unroll
-    for (int h = 0; h < HP; ++h) { m_ref[h] = -INFINITY; l_part[h] = 0.f; }
-    int k_last = -1;            // this group's last tile of the row (index in the group's own tile sequence)
-    bool dead = false;
-
-    for (int c = c_lo + (((c_lo & 1) != grp) ? 1 : 0); c < c_hi; c += NGROUP) {
-      if (dead || *abort_flag) { dead = true; continue; }
-      const int k = c >> 1;                       // tile count of this group, CTA-wide
-      const uint32_t par = (uint32_t)(k & 1);
-      const bool first = (c - c_lo) < NGROUP;     // O holds nothing of this row yet
-      if (!mbar_wait(smem_u32(&sm.t_ready[grp]), par, abort_flag)) { dead = true; continue; }
+  else if (warp < 4) {
+    // ============================= RoPE warps =============================
+    // Thread (warp, lane) owns token 32 warp + lane of every tile, which is tensor-memory lane 32 warp + lane --
+    // the lanes a warp in SM sub-partition `warp` may access.  It turns the K row of product (1) into K' for
+    // product (2); it knows nothing about batch rows.
+    const int tok = tid;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * warp) << 16);
+    int buf = 0;            // accumulator buffer c % 3 and its phase (c / 3) & 1
+    uint32_t bpar = 0;
+    for (int c = 0; c < n_stages; ++c) {
+      if (!mbar_wait(smem_u32(&sm.t_ready[buf]), bpar, abort_flag)) break;
       tc_fence_after();
+      const uint32_t k_addr = lane_addr + TM_K + 128 * buf;
       // ---------------- K row from tensor memory: [RMSNorm,] RoPE, K' back as packed 16-bit pairs ----------------
       float ss = 0.f;
-#pragma unroll 1   // kept rolled: the four warp roles of an SM sub-partition share a small instruction cache
+#pragma unroll 1   // kept rolled: the warp roles of an SM sub-partition share a small instruction cache
       for (int i = 0; i < 8; ++i) {
-        // pairs j = 8i..8i+7: dims j (columns 8i..) and j+64 (columns 64+8i..); table cells 16i..: per two pairs
-        // {cos_j, cos_j+1, sin_j, sin_j+1}
-        float lo[8], hi[8], tg[16];
-        tmem_ld_rope_chunk(lo, hi, tg, k_addr + 8 * i, k_addr + 64 + 8 * i, lane_addr + TM_TRIG + 16 * i);
+        // pairs j = 8i..8i+7: dims j (columns 8i..) and j+64 (columns 64+8i..); table cells 8i..: per two pairs
+        // one word {cos_j, cos_j+1} and one word {sin_j, sin_j+1} in fp16
+        float lo[8], hi[8];
+        uint32_t tg[8];
+        tmem_ld_rope_chunk(lo, hi, tg, k_addr + 8 * i, k_addr + 64 + 8 * i, lane_addr + TM_TRIG + 8 * i);
         if (KNORM) {
           // RMSNorm of K (Qwen3): the weight is applied here, the per-token 1/rms scales the score later
           const float4 w0 = *reinterpret_cast<const float4*>(&sm.knorm_w[8 * i]);
@@ -732,7 +723,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           const float2 L = make_float2(lo[2 * m], lo[2 * m + 1]), H = make_float2(hi[2 * m], hi[2 * m + 1]);
-          const float2 C = make_float2(tg[4 * m], tg[4 * m + 1]), S = make_float2(tg[4 * m + 2], tg[4 * m + 3]);
+          const float2 C = __half22float2(*reinterpret_cast<const __half2*>(&tg[2 * m]));
+          const float2 S = __half22float2(*reinterpret_cast<const __half2*>(&tg[2 * m + 1]));
           const float2 u = __fmul2_rn(H, S);
           const float2 lo2 = __ffma2_rn(L, C, make_float2(-u.x, -u.y));
           const float2 hi2 = __ffma2_rn(L, S, __fmul2_rn(H, C));
@@ -743,18 +735,47 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         tmem_st4(k_addr + 4 * i, plo[0], plo[1], plo[2], plo[3]);
         tmem_st4(k_addr + 64 + 4 * i, phi[0], phi[1], phi[2], phi[3]);
       }
+      if (KNORM) sm.rs_buf[c & 3][tok] = rsqrtf(ss * (1.0f / D) + p.k_norm_eps);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.kp_ready[grp]));
+      if (lane == 0) mbar_arrive(smem_u32(&sm.kp_ready[buf]));
+      if (++buf == NBUF_T) { buf = 0; bpar ^= 1u; }
+    }
+  }
 
+  else if (warp < NCW) {
+  // ============================= softmax warps =============================
+  // Thread (wq, lane) owns token 32 wq + lane of every tile: it reads the token's scores from product (2),
+  // forms the softmax weights against the reference maximum m_ref shared by the four warps, and stores P for
+  // product (3).  These warps follow the batch rows and write each row's result.
+  const int wq = warp & 3;
+  const int tok = 32 * wq + lane;
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * wq) << 16);
+  const uint32_t o_addr = lane_addr + TM_O;
+
+  int row = row0;
+  while (row < p.batch && sm.prefix[row] < u_end) {
+    const int c_lo = max(sm.prefix[row], u_begin) - u_begin;     // tiles of this row in this CTA: [c_lo, c_hi)
+    const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;
+    float m_ref[HP], l_part[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) { m_ref[h] = -INFINITY; l_part[h] = 0.f; }
+    int c_last = -1;            // last tile of the row that was processed
+    bool dead = false;
+
+    for (int c = c_lo; c < c_hi; ++c) {
+      if (dead || *abort_flag) { dead = true; continue; }
+      const int buf = c & 1;
+      const uint32_t par = (uint32_t)((c >> 1) & 1);
+      const bool first = c == c_lo;     // O holds nothing of this row yet
       // ---------------- scores of this token for the group's heads ----------------
-      if (!mbar_wait(smem_u32(&sm.s_ready[grp]), par, abort_flag)) { dead = true; continue; }
+      if (!mbar_wait(smem_u32(&sm.s_ready[buf]), par, abort_flag)) { dead = true; continue; }
       tc_fence_after();
       float s[HP];
-      tmem_ld4(s, s_addr);
+      tmem_ld4(s, lane_addr + TM_S + 16 * buf);
       if (KNORM) {
-        const float rs = rsqrtf(ss * (1.0f / D) + p.k_norm_eps);
+        const float rs = sm.rs_buf[c & 3][tok];
 #pragma unroll
         for (int h = 0; h < HP; ++h) s[h] *= rs;
       }
@@ -765,19 +786,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         if (!valid) s[h] = -INFINITY;
         mx[h] = warp_max_redux(s[h]);
       }
-      // tile maxima: the four warps of the group meet on an mbarrier (bounded wait, unlike a named barrier)
+      // tile maxima: the four warps meet on an mbarrier (bounded wait, unlike a named barrier)
       if (lane == 0) {
-        *reinterpret_cast<float4*>(sm.tmax[grp][par][wq]) = make_float4(mx[0], mx[1], mx[2], mx[3]);
-        mbar_arrive(smem_u32(&sm.grp_sync[grp]));
+        *reinterpret_cast<float4*>(sm.tmax[buf][wq]) = make_float4(mx[0], mx[1], mx[2], mx[3]);
+        mbar_arrive(smem_u32(&sm.grp_sync));
       }
-      if (!mbar_wait(smem_u32(&sm.grp_sync[grp]), par, abort_flag)) { dead = true; continue; }
+      if (!mbar_wait(smem_u32(&sm.grp_sync), (uint32_t)(c & 1), abort_flag)) { dead = true; continue; }
       float factor[HP];
       bool grow = false;
       {
-        const float4 t0 = *reinterpret_cast<const float4*>(sm.tmax[grp][par][0]);
-        const float4 t1 = *reinterpret_cast<const float4*>(sm.tmax[grp][par][1]);
-        const float4 t2 = *reinterpret_cast<const float4*>(sm.tmax[grp][par][2]);
-        const float4 t3 = *reinterpret_cast<const float4*>(sm.tmax[grp][par][3]);
+        const float4 t0 = *reinterpret_cast<const float4*>(sm.tmax[buf][0]);
+        const float4 t1 = *reinterpret_cast<const float4*>(sm.tmax[buf][1]);
+        const float4 t2 = *reinterpret_cast<const float4*>(sm.tmax[buf][2]);
+        const float4 t3 = *reinterpret_cast<const float4*>(sm.tmax[buf][3]);
         const float tm[HP] = {fmaxf(fmaxf(t0.x, t1.x), fmaxf(t2.x, t3.x)), fmaxf(fmaxf(t0.y, t1.y), fmaxf(t2.y, t3.y)),
                               fmaxf(fmaxf(t0.z, t1.z), fmaxf(t2.z, t3.z)), fmaxf(fmaxf(t0.w, t1.w), fmaxf(t2.w, t3.w))};
 #pragma unroll
@@ -790,12 +811,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           }
         }
       }
-      // product (3) of the group's previous tile must be complete before P is overwritten or O rescaled
-      if (k >= 1 && !mbar_wait(smem_u32(&sm.pv_done[grp]), (uint32_t)((k - 1) & 1), abort_flag)) { dead = true; continue; }
-      if (grow) {   // uniform over the group: every thread sees the same maxima
+      // the P tile of this parity was read by product (3) of tile c-2
+      if (c >= 2 && !mbar_wait(smem_u32(&sm.pv_done[buf]), (uint32_t)(((c >> 1) - 1) & 1), abort_flag)) { dead = true; continue; }
+      if (grow) {   // uniform over the four warps: every thread sees the same maxima
 #pragma unroll
         for (int h = 0; h < HP; ++h) l_part[h] *= factor[h];
         if (!first) {
+          // O is rescaled in tensor memory: product (3) of tile c-1 must be complete as well
+          if (!mbar_wait(smem_u32(&sm.pv_done[buf ^ 1]), (uint32_t)(((c - 1) >> 1) & 1), abort_flag)) { dead = true; continue; }
           tc_fence_after();
           float o[4];
           tmem_ld4(o, o_addr);
@@ -810,97 +833,60 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         pr[h] = exp2f(s[h] - (m_ref[h] == -INFINITY ? 0.f : m_ref[h]));
         l_part[h] += pr[h];
       }
-      *reinterpret_cast<uint4*>(sm.p_tile[grp] + tok * 16) = make_uint4(Pack<T>::two(pr[0], pr[1]), Pack<T>::two(pr[2], pr[3]), 0u, 0u);
+      *reinterpret_cast<uint4*>(sm.p_tile[buf] + tok * 16) = make_uint4(Pack<T>::two(pr[0], pr[1]), Pack<T>::two(pr[2], pr[3]), 0u, 0u);
       proxy_fence_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[grp]));
-      k_last = k;
+      if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[buf]));
+      c_last = c;
     }
 
-    // ---------------- row flush: the two groups' partial states are merged ----------------
-    {
-      float o[4] = {0.f, 0.f, 0.f, 0.f};
-      if (k_last >= 0 && !dead && mbar_wait(smem_u32(&sm.pv_done[grp]), (uint32_t)(k_last & 1), abort_flag)) {
-        tc_fence_after();
-        tmem_ld4(o, o_addr);   // O^T[r = tok][head]
-      }
+    // ---------------- row flush ----------------
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    if (c_last >= 0 && !dead && mbar_wait(smem_u32(&sm.pv_done[c_last & 1]), (uint32_t)((c_last >> 1) & 1), abort_flag)) {
+      tc_fence_after();
+      tmem_ld4(o, o_addr);   // O^T[r = tok][head]
+    }
 #pragma unroll
-      for (int h = 0; h < HP; ++h) {
-        sm.merge[grp][h][2 + tok] = o[h];
-        const float l = warp_sum(l_part[h]);
-        if (lane == 0) sm.lsum[grp][wq][h] = l;
-      }
-      if (wq == 0 && lane < HP) sm.merge[grp][lane][0] = m_ref[lane];
+    for (int h = 0; h < HP; ++h) {
+      const float l = warp_sum(l_part[h]);
+      if (lane == 0) sm.lsum[wq][h] = l;
     }
     consumer_bar();
+    float L[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) L[h] = (sm.lsum[0][h] + sm.lsum[1][h]) + (sm.lsum[2][h] + sm.lsum[3][h]);
     const int b = p.batch_index ? p.batch_index[row] : row;
-    const int ctid = tid;  // token threads come first in the block
-    constexpr int N_ITEMS = HP * 128, N_IT = (N_ITEMS + NCW * 32 - 1) / (NCW * 32);
-    float outv[N_IT], L_tot[N_IT], M_tot[N_IT];
-#pragma unroll
-    for (int it = 0; it < N_IT; ++it) {
-      const int item = ctid + it * (NCW * 32);   // (head, r)
-      outv[it] = 0.f; L_tot[it] = 0.f; M_tot[it] = -INFINITY;
-      if (item >= N_ITEMS) continue;
-      const int h = item >> 7, r = item & 127;
-      float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < NGROUP; ++w) M = fmaxf(M, sm.merge[w][h][0]);
-      float v = 0.f, L = 0.f;
-#pragma unroll
-      for (int w = 0; w < NGROUP; ++w) {
-        const float mw = sm.merge[w][h][0];
-        const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-        const float lw = (sm.lsum[w][0][h] + sm.lsum[w][1][h]) + (sm.lsum[w][2][h] + sm.lsum[w][3][h]);
-        v = fmaf(sm.merge[w][h][2 + r], wgt, v);
-        L = fmaf(lw, wgt, L);
-      }
-      outv[it] = v; L_tot[it] = L; M_tot[it] = M;
-    }
     if (!FUSED) {
       // partial record (row, cta) -> entry row + blockIdx.x of this KV head
       float* ws = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.workspace) + ws_header_bytes());
       const size_t entries_per_group = (size_t)p.batch + n_cta;
       float* rec = ws + (((size_t)g * entries_per_group + (size_t)row + blockIdx.x) * HP) * PART_STRIDE;
 #pragma unroll
-      for (int it = 0; it < N_IT; ++it) {
-        const int item = ctid + it * (NCW * 32);
-        if (item >= N_ITEMS) continue;
-        const int h = item >> 7, r = item & 127;
-        rec[h * PART_STRIDE + 2 + r] = outv[it];
-        if (r == 0) { rec[h * PART_STRIDE] = M_tot[it]; rec[h * PART_STRIDE + 1] = L_tot[it]; }
+      for (int h = 0; h < HP; ++h) {
+        rec[h * PART_STRIDE + 2 + tok] = o[h];
+        if (tok == 0) { rec[h * PART_STRIDE] = m_ref[h]; rec[h * PART_STRIDE + 1] = L[h]; }
       }
-      consumer_bar();
+      consumer_bar();   // lsum may be rewritten by the next row
     } else {
-      consumer_bar();   // all reads of merge[] done; reuse merge[0] as the normalised latent [HP][128]
-      float* lat = &sm.merge[0][0][0];
 #pragma unroll
-      for (int it = 0; it < N_IT; ++it) {
-        const int item = ctid + it * (NCW * 32);
-        if (item >= N_ITEMS) continue;
-        const float L = L_tot[it];
-        lat[item] = L > 0.f ? outv[it] / L : 0.f;
-        if (L <= 0.f && (item & 127) == 0 && (item >> 7) < G) set_status(p.status, DKV_ST_EMPTY_ROW);
+      for (int h = 0; h < HP; ++h) {
+        sm.lat[h][tok] = L[h] > 0.f ? o[h] / L[h] : 0.f;
+        if (L[h] <= 0.f && tok == 0 && h < G) set_status(p.status, DKV_ST_EMPTY_ROW);
       }
       consumer_bar();
       const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * D;
-#pragma unroll
-      for (int it = 0; it < N_IT; ++it) {
-        const int item = ctid + it * (NCW * 32);
-        const int h = item >> 7, d = item & 127;
-        if (item < N_ITEMS && h < G) {
-          float o = 0.f;
-          for (int r = 0; r < R; ++r) o = fmaf(lat[h * 128 + r], to_f32(vup[(size_t)r * D + d]), o);
-          T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)(g * G + h) * p.out_stride_h;
-          op[d] = from_f32<T>(o);
-        }
+      for (int h = 0; h < G; ++h) {
+        float acc = 0.f;
+        for (int r = 0; r < R; ++r) acc = fmaf(sm.lat[h][r], to_f32(vup[(size_t)r * D + tok]), acc);
+        T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)(g * G + h) * p.out_stride_h;
+        op[tok] = from_f32<T>(acc);
       }
       consumer_bar();
     }
     ++row;
   }
-  }   // token warps
+  }   // softmax warps
 
   // ---- epilogue: every warp arrives here; the tensor memory is returned by the warp that allocated it ----
   tc_fence_before();

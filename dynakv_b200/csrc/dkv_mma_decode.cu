@@ -5,23 +5,27 @@
 //     evenly over CTAs and writes (m, l, latent accumulator) partials, merged by a combine kernel.
 //
 // A CTA works on 128-token tiles; all three matrix products of a tile run on the 5th-generation tensor
-// core (tcgen05.mma, accumulators in tensor memory), and each of 128 "token threads" owns one token row
-// of the tile (tensor-memory lane = token), so neither RoPE nor the softmax needs a shuffle:
+// core (tcgen05.mma, accumulators in tensor memory), and a token row of the tile belongs to one thread
+// (tensor-memory lane = token), so neither RoPE nor the softmax weights need a shuffle.  The tile pipeline:
 //   2+2 gather warps : copy each token's ragged K / V coefficient row (16-byte cp.async, zero fill past the
-//                      row's length) into K-major, unswizzled 128 x 128 operand tiles in shared memory;
+//                      row's length) into K-major, unswizzled 128 x 128 operand tiles in shared memory; the
+//                      copy engine itself signals the tile's barrier when a lane's copies have landed;
 //   2 MMA threads    : per tile  (1) K = X . Bk          M=128 tokens, N=128, K=128 (A, B from shared memory)
 //                                (2) S = K' . Q~^T       M=128 tokens, N=16,  K=128 (A = K' in tensor memory)
 //                                (3) O^T += XV^T . P     M=128 latent, N=16,  K=128 tokens (accumulates per row);
+//                      one thread issues (1) and (2) from an event loop over barrier probes, another issues (3);
 //                      completion of each product is signalled by tcgen05.commit on mbarriers;
-//   1 rotator warp   : Q~ = scale . R(-s0) q for the tile's base position s0 (the B operand of (2)), so token
-//                      threads rotate K only by their in-tile offset 0..127;
-//   2 x 4 token warps: group g takes tiles of parity g.  A thread reads its token's K row from tensor memory
-//                      (tcgen05.ld.32x32b), applies [RMSNorm and] RoPE in fp32 with its 64 (cos, sin) pairs,
-//                      which also live in tensor memory (they depend on the lane only), and writes K' back as
-//                      packed 16-bit pairs (tcgen05.st) for product (2); then reads its four scores, takes
-//                      p = exp2(s - m_ref) against a per-group reference maximum that is only raised (with a
-//                      rescale of O in tensor memory) when a tile exceeds it by more than 2^8, and stores P
-//                      for product (3).
+//   1 rotator warp   : Q~ = scale . R(-s0) q for the tile's base position s0 (the B operand of (2)), so K is
+//                      rotated only by the in-tile offset 0..127;
+//   4 RoPE warps     : a thread reads its token's K row from one of three accumulator buffers (tcgen05.ld.32x32b),
+//                      applies [RMSNorm and] RoPE in fp32 with its 64 (cos, sin) pairs, which also live in tensor
+//                      memory (fp16 pairs; they depend on the lane only), and writes K' back in place as packed
+//                      16-bit pairs (tcgen05.st) for product (2);
+//   4 softmax warps  : a thread reads its token's four scores, takes p = exp2(s - m_ref) against a reference
+//                      maximum shared by the four warps, which is only raised (with a rescale of O in tensor
+//                      memory) when a tile exceeds it by more than 2^8, and stores P for product (3); these
+//                      warps follow the batch rows and write each row's partial (split) or projected (fused)
+//                      result.
 //
 // Reference math: src/dynakv/kernels/fused.py:28-142 (fused), two_stage.py:52-157,211-281 (two-stage;
 // the latent-space V accumulation with one up-projection at the end is two_stage.py:261-277).
@@ -34,9 +38,9 @@
 namespace dkv {
 
 constexpr int D = 128;
-constexpr int NGROUP = 2;              // token-thread groups: warps 0-3 (even tiles), 4-7 (odd tiles)
-constexpr int NCW = 4 * NGROUP;        // token warps
-// Service warps.  Warp w runs on SM sub-partition w % 4, next to token warps w % 4 and 4 + w % 4; the roles are
+constexpr int NGROUP = 2;              // score tiles / P tiles in flight (tile parity)
+constexpr int NCW = 8;                 // warps 0-3: RoPE stage, warps 4-7: softmax stage
+// Service warps.  Warp w runs on SM sub-partition w % 4, next to RoPE warp w % 4 and softmax warp 4 + w % 4; the roles are
 // placed so that the sub-partitions of the two issuer threads do not also hold the (large) gather code: the
 // instruction caches are small and the issuers' instruction stream is the serial part of the pipeline.
 constexpr int W_KG0 = 8;               // K gather warps 8, 12 (64 tokens of the tile each)

@@ -860,7 +860,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     float L[HP];
 #pragma unroll
     for (int h = 0; h < HP; ++h) L[h] = (sm.lsum[0][h] + sm.lsum[1][h]) + (sm.lsum[2][h] + sm.lsum[3][h]);
-    const int b = p.batch_index ? p.batch_index[row] : row;
     if (!FUSED) {
       // partial record (row, cta) -> entry row + blockIdx.x of this KV head
       float* ws = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.workspace) + ws_header_bytes());
@@ -878,15 +877,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         sm.lat[h][tok] = L[h] > 0.f ? o[h] / L[h] : 0.f;
         if (L[h] <= 0.f && tok == 0 && h < G) set_status(p.status, DKV_ST_EMPTY_ROW);
       }
-      consumer_bar();
-      const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * D;
-      for (int h = 0; h < G; ++h) {
-        float acc = 0.f;
-        for (int r = 0; r < R; ++r) acc = fmaf(sm.lat[h][r], to_f32(vup[(size_t)r * D + tok]), acc);
-        T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)(g * G + h) * p.out_stride_h;
-        op[tok] = from_f32<T>(acc);
-      }
-      consumer_bar();
+      // the up-projection is done by the whole block after the pipeline has drained (a fused CTA has one row)
     }
     ++row;
   }
@@ -895,6 +886,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   // ---- epilogue: every warp arrives here; the tensor memory is returned by the warp that allocated it ----
   tc_fence_before();
   __syncthreads();
+  if (FUSED) {
+    // out[head][d] = sum_r latent[head][r] * Bv[r][d]: one output element per thread
+    const int h = tid >> 7, d = tid & 127;
+    if (h < G) {
+      const int b = p.batch_index ? p.batch_index[blockIdx.x] : blockIdx.x;
+      const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * D + d;
+      float acc0 = 0.f, acc1 = 0.f;
+      int r = 0;
+      for (; r + 1 < R; r += 2) {
+        acc0 = fmaf(sm.lat[h][r], to_f32(vup[(size_t)r * D]), acc0);
+        acc1 = fmaf(sm.lat[h][r + 1], to_f32(vup[(size_t)(r + 1) * D]), acc1);
+      }
+      if (r < R) acc0 = fmaf(sm.lat[h][r], to_f32(vup[(size_t)r * D]), acc0);
+      T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)(g * G + h) * p.out_stride_h;
+      op[d] = from_f32<T>(acc0 + acc1);
+    }
+  }
   if (warp == W_MMA) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));

@@ -66,6 +66,30 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Programmatic dependent launch.  The kernel after this one in the stream may be scheduled as soon as every CTA
+// of this one has called launch_dependents (or exited); it must call wait before touching anything the kernel
+// before it writes -- wait returns when that kernel has completed and its writes are visible.  Both are no-ops
+// when the launch did not ask for programmatic serialization.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with the programmatic-serialization attribute: the kernel may start while its predecessor in the stream
+// is still running, up to its pdl_wait().  Works under stream capture (the edge becomes a programmatic one).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 __device__ __forceinline__ void set_status(int32_t* status, int32_t bit) {
   if (status != nullptr) atomicOr(status, bit);
 }

@@ -307,68 +307,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   const int R = p.rank;
   volatile int* abort_flag = &sm.abort_flag;
 
-  // ---- prologue A: partition table and barriers --------------------------------------------------
-  if (warp == 0) {
-    // inclusive scan of the per-row tile counts, 32 rows at a time
-    int carry = 0;
-    for (int base = 0; base < p.batch; base += 32) {
-      const int i = base + lane;
-      int v = (i < p.batch) ? (row_tokens(p, i) + ST_TOK - 1) / ST_TOK : 0;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, v, o);
-        if (lane >= o) v += t;
-      }
-      if (i < p.batch) sm.prefix[i + 1] = carry + v;
-      carry += __shfl_sync(0xffffffffu, v, 31);
+  // ---- prologue A: everything that does not depend on the kernel before this one -----------------------
+  // (programmatic dependent launch: this part overlaps the tail of the preceding kernel in the stream, which
+  // may still be appending this step's token; the kernel after this one may start its own independent part now)
+  pdl_launch_dependents();
+  if (tid == 0) {
+    sm.prefix[0] = 0;
+    sm.abort_flag = 0;
+    for (int s = 0; s < NBUF_A; ++s) { mbar_init(smem_u32(&sm.a_full[s]), 64); mbar_init(smem_u32(&sm.a_free[s]), 1); }
+    for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 64); mbar_init(smem_u32(&sm.v_free[s]), 1); }
+    for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 1); mbar_init(smem_u32(&sm.q_free[s]), 1); }
+    for (int s = 0; s < NGROUP; ++s) {
+      mbar_init(smem_u32(&sm.s_ready[s]), 1);
+      mbar_init(smem_u32(&sm.p_ready[s]), 4);
+      mbar_init(smem_u32(&sm.pv_done[s]), 1);
     }
-    if (lane == 0) {
-      sm.prefix[0] = 0;
-      sm.abort_flag = 0;
-      for (int s = 0; s < NBUF_A; ++s) { mbar_init(smem_u32(&sm.a_full[s]), 64); mbar_init(smem_u32(&sm.a_free[s]), 1); }
-      for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 64); mbar_init(smem_u32(&sm.v_free[s]), 1); }
-      for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 1); mbar_init(smem_u32(&sm.q_free[s]), 1); }
-      for (int s = 0; s < NGROUP; ++s) {
-        mbar_init(smem_u32(&sm.s_ready[s]), 1);
-        mbar_init(smem_u32(&sm.p_ready[s]), 4);
-        mbar_init(smem_u32(&sm.pv_done[s]), 1);
-      }
-      for (int s = 0; s < NBUF_T; ++s) { mbar_init(smem_u32(&sm.t_ready[s]), 1); mbar_init(smem_u32(&sm.kp_ready[s]), 4); }
-      mbar_init(smem_u32(&sm.grp_sync), 4);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
+    for (int s = 0; s < NBUF_T; ++s) { mbar_init(smem_u32(&sm.t_ready[s]), 1); mbar_init(smem_u32(&sm.kp_ready[s]), 4); }
+    mbar_init(smem_u32(&sm.grp_sync), 4);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
-
-  const int total_units = sm.prefix[p.batch];
-  int u_begin, u_end;
-  if (FUSED) {
-    u_begin = sm.prefix[blockIdx.x];
-    u_end = sm.prefix[blockIdx.x + 1];
-  } else {
-    u_begin = unit_begin(blockIdx.x, n_cta, total_units);
-    u_end = unit_begin(blockIdx.x + 1, n_cta, total_units);
-    if (blockIdx.x == 0 && g == 0 && p.workspace) {
-      WsHeader* wh = reinterpret_cast<WsHeader*>(p.workspace);
-      for (int i = tid; i <= p.batch; i += NTHREADS) wh->prefix[i] = sm.prefix[i];
-      if (tid == 0) { wh->total_units = total_units; wh->n_cta = n_cta; }
-    }
-  }
-  const int n_stages = u_end - u_begin;
-
-  if (FUSED && n_stages <= 0) {
-    // row without tokens: zeros, flagged
-    for (int e = tid; e < G * D; e += NTHREADS) {
-      const int b = p.batch_index ? p.batch_index[blockIdx.x] : blockIdx.x;
-      T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)(g * G + e / D) * p.out_stride_h;
-      op[e % D] = from_f32<T>(0.f);
-    }
-    if (tid == 0) set_status(p.status, DKV_ST_EMPTY_ROW);
-    return;
-  }
-  if (n_stages <= 0) return;
-
-  // ---- prologue B: basis, tensor memory, RoPE table (only CTAs that have work) --------------------
   {
     // basis rows [R][128] -> the MN-major unswizzled operand layout of the tensor core: 8x8 core matrices,
     // element (r, d) at (r/8)*2048 + (d/8)*128 + (r%8)*16 + (d%8)*2; rows >= R are zero
@@ -386,8 +343,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
     // RoPE table for the in-tile offsets t = 0..127: angle = t * f_j, f_j = exp(-(2j/D) ln theta), staged as
     // 16-bit cells tr[t][4*(j/2) + (j&1)] = cos, [.. + 2] = sin (row pitch 130 cells = 65 words): per two pairs one
-    // word of cosines and one of sines, kept in fp16 (2^-11 absolute, below the 16-bit rounding of K').  NTHREADS is a multiple of 64, so a
-    // thread keeps one j and steps t by NTHREADS/64: one exact sincos, then a fixed-angle rotation per step.
+    // word of cosines and one of sines, kept in fp16 (2^-11 absolute, below the 16-bit rounding of K').
+    // NTHREADS is a multiple of 64, so a thread keeps one j and steps t by NTHREADS/64: one exact sincos, then a
+    // fixed-angle rotation per step.
     static_assert(NTHREADS % 64 == 0, "trig table fill assumes a fixed j per thread");
     constexpr int TSTEP = NTHREADS / 64;
     __half* tr = reinterpret_cast<__half*>(sm.v_tile[0]);   // spans the (contiguous) V tiles until the pipeline starts
@@ -406,12 +364,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     if (KNORM && tid < D) sm.knorm_w[tid] = p.k_norm_weight[tid];
     for (int e = tid; e < NQ * Q_TILE_BYTES / 4; e += NTHREADS) reinterpret_cast<uint32_t*>(sm.qrot)[e] = 0u;   // rows the rotator never writes
   }
+
+  // ---- prologue B: partition table (cache lengths: written by the kernel before this one) ----------------
+  pdl_wait();
+  if (warp == 0) {
+    // inclusive scan of the per-row tile counts, 32 rows at a time
+    int carry = 0;
+    for (int base = 0; base < p.batch; base += 32) {
+      const int i = base + lane;
+      int v = (i < p.batch) ? (row_tokens(p, i) + ST_TOK - 1) / ST_TOK : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+      }
+      if (i < p.batch) sm.prefix[i + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
   if (warp < 4) {
-    // the table row of this thread's local offset goes to its tensor-memory lane (both groups read it there)
+    // the table row of this thread's in-tile offset goes to its tensor-memory lane
     const float* tr = reinterpret_cast<const float*>(sm.v_tile[0]) + tid * 65;   // 64 packed words of this row
     const uint32_t dst = tmem_base + ((uint32_t)(32 * warp) << 16) + TM_TRIG;
 #pragma unroll
@@ -427,6 +403,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+
+  const int total_units = sm.prefix[p.batch];
+  int u_begin, u_end;
+  if (FUSED) {
+    u_begin = sm.prefix[blockIdx.x];
+    u_end = sm.prefix[blockIdx.x + 1];
+  } else {
+    u_begin = unit_begin(blockIdx.x, n_cta, total_units);
+    u_end = unit_begin(blockIdx.x + 1, n_cta, total_units);
+    if (blockIdx.x == 0 && g == 0 && p.workspace) {
+      WsHeader* wh = reinterpret_cast<WsHeader*>(p.workspace);
+      for (int i = tid; i <= p.batch; i += NTHREADS) wh->prefix[i] = sm.prefix[i];
+      if (tid == 0) { wh->total_units = total_units; wh->n_cta = n_cta; }
+    }
+  }
+  const int n_stages = u_end - u_begin;
+  bool project = FUSED;   // fused path: the block projects its row at the end
+
+  if (FUSED && n_stages <= 0) {
+    // row without tokens: zeros, flagged
+    for (int e = tid; e < G * D; e += NTHREADS) {
+      const int b = p.batch_index ? p.batch_index[blockIdx.x] : blockIdx.x;
+      T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)(g * G + e / D) * p.out_stride_h;
+      op[e % D] = from_f32<T>(0.f);
+    }
+    if (tid == 0) set_status(p.status, DKV_ST_EMPTY_ROW);
+    project = false;
+  }
 
   // first batch row touched by this CTA
   int row0 = 0;
@@ -446,7 +450,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     ri.first_unit = sm.prefix[ri.row];
   };
 
-  if (warp == W_ROT) {
+  if (n_stages <= 0) {
+    // nothing to do for this CTA (fewer tiles than CTAs, or an empty row): straight to the epilogue
+  }
+  else if (warp == W_ROT) {
     // =========================== query rotator warp ===========================
     // For every tile (base position s0) it publishes Q~ = scale * R(-s0) q for the group's heads as rows 0..3 of
     // the B operand of product (2), so that q~ . R(t) k = q . R(s0 + t) k with the in-tile offset t = 0..127
@@ -886,7 +893,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   // ---- epilogue: every warp arrives here; the tensor memory is returned by the warp that allocated it ----
   tc_fence_before();
   __syncthreads();
-  if (FUSED) {
+  if (project) {
     // out[head][d] = sum_r latent[head][r] * Bv[r][d]: one output element per thread
     const int h = tid >> 7, d = tid & 127;
     if (h < G) {
@@ -916,6 +923,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 constexpr int COMBINE_MAX_PART = 160;   // >= CTAs per KV head (at most the SM count)
 template <typename T>
 __global__ void __launch_bounds__(128) split_combine_kernel(dkv_attn_args p) {
+  pdl_launch_dependents();
+  pdl_wait();   // the partial records come from the split kernel before this one
   __shared__ float lat_s[128];
   __shared__ float wgt_s[COMBINE_MAX_PART];
   __shared__ float red_s[4][128];
@@ -1047,13 +1056,13 @@ static int launch_mma(const dkv_attn_args* a, int n_cta) {
   if (a->k_norm_weight) {
     auto kern = mma_decode_kernel<T, FUSED, true>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta);
+    if (e == cudaSuccess) e = launch_pdl(kern, grid, dim3(NTHREADS), smem, st, *a, log_theta, n_cta);
   } else {
     auto kern = mma_decode_kernel<T, FUSED, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) kern<<<grid, NTHREADS, smem, st>>>(*a, log_theta, n_cta);
+    if (e == cudaSuccess) e = launch_pdl(kern, grid, dim3(NTHREADS), smem, st, *a, log_theta, n_cta);
   }
-  DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+  DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "launch of the decode kernel failed: %s", cudaGetErrorString(e));
   DKV_CHECK_LAUNCH();
   return DKV_OK;
 }
@@ -1077,8 +1086,9 @@ int mma_combine(const dkv_attn_args* a) {
   DKV_REQUIRE(a->workspace != nullptr, DKV_E_WORKSPACE, "combine needs the split workspace");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
   dim3 grid(a->batch, a->n_q_heads);
-  if (a->dtype == DKV_BF16) split_combine_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(*a);
-  else split_combine_kernel<__half><<<grid, 128, 0, st>>>(*a);
+  cudaError_t e = a->dtype == DKV_BF16 ? launch_pdl(split_combine_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, *a)
+                                       : launch_pdl(split_combine_kernel<__half>, grid, dim3(128), 0, st, *a);
+  DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "launch of the combine kernel failed: %s", cudaGetErrorString(e));
   DKV_CHECK_LAUNCH();
   return DKV_OK;
 }

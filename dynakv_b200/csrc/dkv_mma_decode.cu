@@ -83,11 +83,9 @@ struct SmemLayout {
   alignas(16) float knorm_w[D];
   uint32_t kvalid[KV_RING][4];                              // bit l of word w: token 32w + l of the tile has a K row
   alignas(8) unsigned long long a_full[NBUF_A];    // K operand tile written (2 gather warps)
-  alignas(8) unsigned long long a_free[NBUF_A];    // product (1) done with it (commit)
   alignas(8) unsigned long long v_full[NBUF_V];    // V operand tile written (2 gather warps)
   alignas(8) unsigned long long v_free[NBUF_V];    // product (3) done with it (commit)
   alignas(8) unsigned long long q_full[NQ];        // rotated queries written (rotator)
-  alignas(8) unsigned long long q_free[NQ];        // product (2) done with them (commit)
   alignas(8) unsigned long long t_ready[NBUF_T];   // K accumulator written (commit)
   alignas(8) unsigned long long kp_ready[NBUF_T];  // K' written back to tensor memory (4 RoPE warps)
   alignas(8) unsigned long long s_ready[NGROUP];   // scores written (commit)
@@ -314,9 +312,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   if (tid == 0) {
     sm.prefix[0] = 0;
     sm.abort_flag = 0;
-    for (int s = 0; s < NBUF_A; ++s) { mbar_init(smem_u32(&sm.a_full[s]), 64); mbar_init(smem_u32(&sm.a_free[s]), 1); }
+    for (int s = 0; s < NBUF_A; ++s) mbar_init(smem_u32(&sm.a_full[s]), 64);
     for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 64); mbar_init(smem_u32(&sm.v_free[s]), 1); }
-    for (int s = 0; s < NQ; ++s) { mbar_init(smem_u32(&sm.q_full[s]), 1); mbar_init(smem_u32(&sm.q_free[s]), 1); }
+    for (int s = 0; s < NQ; ++s) mbar_init(smem_u32(&sm.q_full[s]), 1);
     for (int s = 0; s < NGROUP; ++s) {
       mbar_init(smem_u32(&sm.s_ready[s]), 1);
       mbar_init(smem_u32(&sm.p_ready[s]), 4);
@@ -468,7 +466,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     int row = row0;
     for (int c = 0; c < n_stages; ++c) {
       const int slot = c % NQ;
-      if (c >= NQ && !mbar_wait(smem_u32(&sm.q_free[slot]), (uint32_t)(((c / NQ) - 1) & 1), abort_flag)) break;
+      // the slot was read by product (2) of tile c-2, whose completion is s_ready of that tile
+      if (c >= NQ && !mbar_wait(smem_u32(&sm.s_ready[slot]), (uint32_t)(((c / NQ) - 1) & 1), abort_flag)) break;
       const int u = u_begin + c;
       while (u >= sm.prefix[row + 1]) ++row;
       const bool row_start = (c == 0) || (u == sm.prefix[row]);
@@ -563,7 +562,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         if (lane == 0) { sm.kvalid[c % KV_RING][2 * gw] = m0; sm.kvalid[c % KV_RING][2 * gw + 1] = m1; }
       }
       // the tensor core must be done with the tile that was in this buffer NB tiles ago
-      if (c >= NB && !mbar_wait(smem_u32(is_v ? &sm.v_free[buf] : &sm.a_free[buf]), (uint32_t)(((c / NB) - 1) & 1), abort_flag)) break;
+      // (K: product (1) of tile c-2 read this buffer; its completion is t_ready of that tile, ring of NBUF_T)
+      if (c >= NB) {
+        const uint32_t bar = is_v ? smem_u32(&sm.v_free[buf]) : smem_u32(&sm.t_ready[(c - NBUF_A) % NBUF_T]);
+        const uint32_t par = is_v ? (uint32_t)(((c / NBUF_V) - 1) & 1) : (uint32_t)(((c - NBUF_A) / NBUF_T) & 1);
+        if (!mbar_wait(bar, par, abort_flag)) break;
+      }
       unsigned char* const tile = is_v ? sm.v_tile[buf] : sm.a_tile[buf];
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
@@ -622,8 +626,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
             umma_f16(tmem_base + TM_K + rt * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
                      umma_desc(basis_addr + ks * 4096, 2048, 128), idesc_k, ks > 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&sm.t_ready[rt]));
-          umma_commit(smem_u32(&sm.a_free[rb]));
+          umma_commit(smem_u32(&sm.t_ready[rt]));   // also frees the operand tile (the K gather warps wait on it too)
           ++ri;
           if (++rt == NBUF_T) { rt = 0; rtp ^= 1u; }
           progress = true;
@@ -639,8 +642,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
             umma_f16_ta(tmem_base + TM_S + 16 * qg, kp + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4)),
                         umma_desc(q_addr + ks * 2 * Q_LBO, Q_LBO, 128), idesc_s, ks > 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&sm.s_ready[qg]));
-          umma_commit(smem_u32(&sm.q_free[qg]));
+          umma_commit(smem_u32(&sm.s_ready[qg]));   // also frees the rotated queries (the rotator waits on it too)
           ++qi;
           if (++qt == NBUF_T) { qt = 0; qtp ^= 1u; }
           progress = true;

@@ -77,8 +77,7 @@ __global__ void __launch_bounds__(512) append_decode_kernel(dkv_append_args p) {
 // interleaved shuffles, so eight independent L2 loads are in flight per lane.
 template <typename T>
 __global__ void __launch_bounds__(1024) append_project_kernel(dkv_append_args p, int wpi) {
-  pdl_launch_dependents();   // the attention kernel after this one may start its set-up now ...
-  pdl_wait();                // ... and this one touches the cache only after the kernel before it is done
+  pdl_launch_dependents();   // the attention kernel after this one may start its set-up (which reads no cache state) now
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int A = p.arenas_per_batch;
@@ -252,7 +251,7 @@ extern "C" int dkv_append_decode(const dkv_append_args* a) {
                 "dkv_append_decode: in-kernel projection needs 128-wide 16-bit rows and at most 16 arenas per batch row");
 #define LAUNCH(T)                                                             \
   do {                                                                        \
-    if (proj) launch_pdl(append_project_kernel<T>, dim3(a->batch), dim3(32 * wpi * items), 0, st, *a, wpi); \
+    if (proj) append_project_kernel<T><<<a->batch, 32 * wpi * items, 0, st>>>(*a, wpi); \
     else append_decode_kernel<T, false><<<a->batch, threads, 0, st>>>(*a);    \
   } while (0)
   if (a->dtype == DKV_F32) LAUNCH(float);

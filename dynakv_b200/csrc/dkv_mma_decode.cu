@@ -307,8 +307,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 
   // ---- prologue A: everything that does not depend on the kernel before this one -----------------------
   // (programmatic dependent launch: this part overlaps the tail of the preceding kernel in the stream, which
-  // may still be appending this step's token; the kernel after this one may start its own independent part now)
-  pdl_launch_dependents();
+  // may still be appending this step's token)
   if (tid == 0) {
     sm.prefix[0] = 0;
     sm.abort_flag = 0;
@@ -925,8 +924,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 constexpr int COMBINE_MAX_PART = 160;   // >= CTAs per KV head (at most the SM count)
 template <typename T>
 __global__ void __launch_bounds__(128) split_combine_kernel(dkv_attn_args p) {
-  pdl_launch_dependents();
-  pdl_wait();   // the partial records come from the split kernel before this one
   __shared__ float lat_s[128];
   __shared__ float wgt_s[COMBINE_MAX_PART];
   __shared__ float red_s[4][128];
@@ -1088,9 +1085,10 @@ int mma_combine(const dkv_attn_args* a) {
   DKV_REQUIRE(a->workspace != nullptr, DKV_E_WORKSPACE, "combine needs the split workspace");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
   dim3 grid(a->batch, a->n_q_heads);
-  cudaError_t e = a->dtype == DKV_BF16 ? launch_pdl(split_combine_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, *a)
-                                       : launch_pdl(split_combine_kernel<__half>, grid, dim3(128), 0, st, *a);
-  DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "launch of the combine kernel failed: %s", cudaGetErrorString(e));
+  // launched the ordinary way: measured, an early (programmatic) launch of the combine or of the next append
+  // costs more than it hides -- their CTAs wait on the SMs the decode kernel is using
+  if (a->dtype == DKV_BF16) split_combine_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(*a);
+  else split_combine_kernel<__half><<<grid, 128, 0, st>>>(*a);
   DKV_CHECK_LAUNCH();
   return DKV_OK;
 }

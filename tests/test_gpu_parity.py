@@ -321,3 +321,36 @@ def test_linearity_in_values():
     case.v.flat.mul_(2.0)
     out2 = two_stage_attention(*_case_args(case), len_multiple=8).float()
     assert (out2 - 2.0 * out1).abs().max().item() <= 2.0 * 2.0 ** -8 * out1.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_reference_maximum_is_raised_late_in_a_row(dtype):
+    # The scores of the last third of the row are far larger than anything before (K coefficients x 24):
+    # the softmax reference has to be raised, and the accumulated O rescaled, well after the first tile --
+    # in the fused kernel (one CTA walks the row) and in the split kernel (the jump falls inside a CTA's range).
+    seq = 1536
+    case = synthetic.make_layer_case(91, [seq, 900], "beta:2,5", 500000.0, dtype, DEV, n_q_heads=8, n_kv_heads=2)
+    fk, fv, lk, lv, ok, ov = case.views()
+    rows = fk.shape[0]
+    for r in range(rows):
+        start = int(ok[r, 1000].item())          # first coefficient of token 1000 of this arena row
+        fk[r, start:] *= 24.0
+    ref = _case_oracle(case)
+    sl = torch.tensor(case.seq_lens, dtype=torch.int32, device=DEV)
+    for fn in (fused_attention_dispatch, two_stage_attention):
+        out = fn(*_case_args(case), seq_lens=sl, len_multiple=8)
+        _check16(out, ref)
+    assert _common.read_status(torch.device(DEV)) == 0
+
+
+def test_many_short_rows_share_a_split_cta():
+    # 40 rows of 1..3 tiles: in the split kernel most CTAs cover several batch rows (row flushes in the middle of
+    # a CTA's tile sequence, first-tile flags, partial records of rows that end and begin inside one CTA)
+    gen = torch.Generator().manual_seed(77)
+    seq_lens = torch.randint(1, 384, (40,), generator=gen).tolist()
+    case = synthetic.make_layer_case(78, seq_lens, "beta:2,5", 10000.0, torch.bfloat16, DEV, n_q_heads=8, n_kv_heads=2)
+    ref = _case_oracle(case)
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    out = two_stage_attention(*_case_args(case), seq_lens=sl, len_multiple=8)
+    _check16(out, ref)
+    assert _common.read_status(torch.device(DEV)) == 0

@@ -22,7 +22,7 @@ _DTYPES = {torch.float32: DKV_F32, torch.float16: DKV_F16, torch.bfloat16: DKV_B
 EXPORTS = (
     "dkv_version", "dkv_last_error", "dkv_fused_decode", "dkv_split_workspace_bytes", "dkv_split_decode",
     "dkv_split_combine", "dkv_two_stage_decode", "dkv_two_stage_decode_noalloc", "dkv_scores", "dkv_softmax_v", "dkv_append_decode",
-    "dkv_pack_bulk", "dkv_decompress",
+    "dkv_pack_bulk", "dkv_decompress", "dkv_gate_lengths", "dkv_gate_workspace_bytes",
 )
 
 
@@ -73,6 +73,16 @@ class PackArgs(C.Structure):
     ]
 
 
+class GateArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32), ("n_rows", C.c_int32), ("dim", C.c_int32), ("low_rank", C.c_int32),
+        ("threshold", C.c_float),
+        ("x", C.c_void_p), ("x_stride", C.c_int64), ("w", C.c_void_p), ("b", C.c_void_p),
+        ("lengths", C.c_void_p), ("masked", C.c_void_p), ("masked_stride", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+    ]
+
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -103,6 +113,10 @@ def load() -> C.CDLL:
     lib.dkv_pack_bulk.restype = C.c_int
     lib.dkv_decompress.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(Side), C.c_void_p, C.c_void_p]
     lib.dkv_decompress.restype = C.c_int
+    lib.dkv_gate_lengths.argtypes = [C.POINTER(GateArgs)]
+    lib.dkv_gate_lengths.restype = C.c_int
+    lib.dkv_gate_workspace_bytes.argtypes = [C.POINTER(GateArgs)]
+    lib.dkv_gate_workspace_bytes.restype = C.c_size_t
     _lib = lib
     return lib
 

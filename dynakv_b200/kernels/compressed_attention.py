@@ -28,6 +28,50 @@ def merge_basis(up: torch.Tensor, n_kv_heads: int, head_dim: int, low_rank: Opti
     return up[:, :rank].reshape(n_kv_heads, head_dim, rank).transpose(1, 2).contiguous()
 
 
+def gate_lengths(states: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, low_rank: int,
+                 threshold: float = 0.1, return_masked: bool = True):
+    """Cutoff gate of one side (kernels/compressed_attention.py:84-119, one of the two halves of
+    ``kv_process_fused``): ``states`` [..., d] spectral coefficient rows, ``weight`` [d, d], ``bias`` [d] or [1, d].
+
+    Returns (masked states or None, lengths int32 [...]): lengths[t] = #{i < low_rank : cumsum(softmax(x W + b))
+    [d-1-i] >= threshold}, masked = states with everything past the length zeroed.  fp32 arithmetic.
+    """
+    if not states.is_cuda:
+        raise RuntimeError("dynakv_b200 has no CPU path: the gate needs CUDA tensors")
+    d = states.shape[-1]
+    if weight.shape != (d, d) or bias.numel() != d:
+        raise ValueError(f"gate weight must be [{d}, {d}] and bias [{d}], got {tuple(weight.shape)} and {tuple(bias.shape)}")
+    if weight.dtype != states.dtype or bias.dtype != states.dtype:
+        raise ValueError("gate weight, bias and states must share a dtype")
+    x = states.reshape(-1, d)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    w, b = weight.contiguous(), bias.reshape(-1).contiguous()
+    lengths = torch.empty(x.shape[0], dtype=torch.int32, device=states.device)
+    masked = torch.empty((x.shape[0], d), dtype=states.dtype, device=states.device) if return_masked else None
+    a = _lib.GateArgs()
+    a.dtype, a.n_rows, a.dim, a.low_rank, a.threshold = _lib.dtype_code(states.dtype), x.shape[0], d, int(low_rank), threshold
+    a.x, a.x_stride, a.w, a.b = x.data_ptr(), x.stride(0), w.data_ptr(), b.data_ptr()
+    a.lengths = lengths.data_ptr()
+    a.masked, a.masked_stride = (masked.data_ptr(), masked.stride(0)) if return_masked else (None, 0)
+    lib = _lib.load()
+    need = lib.dkv_gate_workspace_bytes(C.byref(a))
+    scratch = torch.empty(max(need, 4) // 4, dtype=torch.float32, device=states.device)
+    a.workspace, a.workspace_bytes = scratch.data_ptr(), scratch.numel() * 4
+    a.stream = _lib.stream_ptr(states.device)
+    _lib.check(lib.dkv_gate_lengths(C.byref(a)), "dkv_gate_lengths")
+    lead = states.shape[:-1]
+    return (masked.reshape(*lead, d) if return_masked else None), lengths.reshape(lead)
+
+
+def kv_process_fused(key_states: torch.Tensor, value_states: torch.Tensor, Wk, bk, Wv, bv, low_rank: int):
+    """Drop-in for the reference module method of the same name (kernels/compressed_attention.py:84-119):
+    returns (k_out, v_out, len_k, len_v, 1, 1) for key_states / value_states [B, S, d]."""
+    k_out, len_k = gate_lengths(key_states, Wk, bk, low_rank)
+    v_out, len_v = gate_lengths(value_states, Wv, bv, low_rank)
+    return k_out, v_out, len_k, len_v, 1, 1
+
+
 class CompressedDecodeLayer:
     """One attention layer's decode step on the compressed cache (per-KV-head arenas)."""
 

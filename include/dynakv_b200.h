@@ -191,6 +191,31 @@ int dkv_pack_bulk(const dkv_pack_args* a);
 int dkv_decompress(int32_t dtype, int32_t n_arena, int32_t n_tok, int32_t max_dim, const dkv_side* side,
                    void* dense, void* stream);
 
+/* ---- cutoff gate ------------------------------------------------------- */
+/* Kept-coefficient count of token rows: logits = b + x.W, p = softmax(logits), c = cumsum(p),
+ * length = #{ i < low_rank : c[dim-1-i] >= threshold } (threshold 0.1 in the reference); optionally the
+ * rows with everything past their length zeroed.  fp32 arithmetic for every storage type.
+ * Replaces kv_process_fused -- src/dynakv/kernels/compressed_attention.py:84-119 (one side, K or V, per call). */
+typedef struct dkv_gate_args {
+  int32_t dtype;          /* DKV_F32 / DKV_F16 / DKV_BF16: type of x, w, b, masked */
+  int32_t n_rows;         /* token rows */
+  int32_t dim;            /* width of a row = rows and columns of w (<= 1024) */
+  int32_t low_rank;       /* positions >= low_rank never count */
+  float threshold;
+  const void* x;          /* [n_rows, dim] */
+  int64_t x_stride;       /* elements between rows */
+  const void* w;          /* [dim, dim] row-major */
+  const void* b;          /* [dim] */
+  int32_t* lengths;       /* out [n_rows] */
+  void* masked;           /* out [n_rows, dim] or NULL */
+  int64_t masked_stride;
+  void* workspace;        /* fp32 scratch of dkv_gate_workspace_bytes(args) bytes */
+  size_t workspace_bytes;
+  void* stream;
+} dkv_gate_args;
+size_t dkv_gate_workspace_bytes(const dkv_gate_args* args);
+int dkv_gate_lengths(const dkv_gate_args* args);
+
 /* ---- misc -------------------------------------------------------------- */
 int dkv_version(void);
 const char* dkv_last_error(void);

@@ -354,3 +354,44 @@ def test_many_short_rows_share_a_split_cta():
     out = two_stage_attention(*_case_args(case), seq_lens=sl, len_multiple=8)
     _check16(out, ref)
     assert _common.read_status(torch.device(DEV)) == 0
+
+
+# ------------------------------------------------------------------ cutoff gate
+def _gate_margin_ok(x, W, b, thr=0.1, margin=2e-5):
+    """rows whose decision is not within `margin` of the threshold anywhere (a different summation order may flip those)"""
+    c = torch.softmax(torch.addmm(b.reshape(-1).double(), x.double(), W.double()), dim=-1).cumsum(-1)
+    return ((c - thr).abs() > margin).all(dim=-1)
+
+
+def test_gate_matches_reference_fixture():
+    from dynakv_b200.kernels.compressed_attention import kv_process_fused
+    g = load_golden("gate_d64")
+    k, v = torch.from_numpy(g["k"]).to(DEV), torch.from_numpy(g["v"]).to(DEV)
+    d = k.shape[-1]
+    Wk, bk, Wv, bv = (torch.from_numpy(g[n]).to(DEV) for n in ("Wk", "bk", "Wv", "bv"))
+    k_out, v_out, len_k, len_v, _, _ = kv_process_fused(k, v, Wk, bk, Wv, bv, int(g["low_rank"]) if "low_rank" in g else d)
+    ok_k = _gate_margin_ok(k.reshape(-1, d).cpu(), Wk.cpu(), bk.cpu()).reshape(len_k.shape)
+    ok_v = _gate_margin_ok(v.reshape(-1, d).cpu(), Wv.cpu(), bv.cpu()).reshape(len_v.shape)
+    assert ok_k.float().mean() > 0.9
+    assert torch.equal(len_k.cpu()[ok_k], torch.from_numpy(g["len_k"]).to(torch.int32)[ok_k])
+    assert torch.equal(len_v.cpu()[ok_v], torch.from_numpy(g["len_v"]).to(torch.int32)[ok_v])
+    assert torch.equal(k_out.cpu()[ok_k], torch.from_numpy(g["k_out"])[ok_k])
+
+
+@pytest.mark.parametrize("dtype,d,low_rank,rows", [(torch.float32, 1024, 1024, 37), (torch.bfloat16, 1024, 640, 37),
+                                                   (torch.float16, 128, 128, 37), (torch.float32, 200, 96, 37),
+                                                   (torch.bfloat16, 1024, 1024, 3), (torch.float32, 512, 300, 2)])
+def test_gate_against_oracle(dtype, d, low_rank, rows):
+    # rows * 3 <= 64 takes the decode-shaped path (reduction cut in chunks, weight tiles staged in shared memory)
+    from dynakv_b200.kernels.compressed_attention import gate_lengths
+    gen = torch.Generator().manual_seed(11 + d)
+    x = (torch.randn(3, rows, d, generator=gen) * 2).to(dtype)
+    W = (torch.randn(d, d, generator=gen) / d ** 0.5).to(dtype)
+    b = (torch.randn(d, generator=gen) * 0.5).to(dtype)
+    ref = O.gate_lengths(x.reshape(-1, d).float(), W.float(), b.float(), low_rank).reshape(3, rows)
+    masked, lens = gate_lengths(x.to(DEV), W.to(DEV), b.to(DEV), low_rank)
+    ok = _gate_margin_ok(x.reshape(-1, d).float(), W.float(), b.float()).reshape(3, rows)
+    assert ok.float().mean() > 0.8
+    assert torch.equal(lens.cpu()[ok], ref[ok])
+    keep = torch.arange(d)[None, None, :] < lens.cpu()[..., None]
+    assert torch.equal(masked.cpu(), torch.where(keep, x, torch.zeros_like(x)))

@@ -575,8 +575,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         const uint32_t dst = smem_u32(tile) + (tA + 32 * k) * 16;
 #pragma unroll
         for (int ch = 0; ch < 16; ++ch) {
-          const bool in = ch * 8 < len[k];
-          cp_async16_zfill(dst + ch * 2048, in ? row_src + ch * 16 : row_src, in ? 16 : 0);
+          // past the row's length the source size is 0: nothing is read from the (then meaningless) address
+          cp_async16_zfill(dst + ch * 2048, row_src + ch * 16, ch * 8 < len[k] ? 16 : 0);
         }
       }
       // The tile is handed over by the copy engine itself: each lane's arrival on the tile's barrier fires when

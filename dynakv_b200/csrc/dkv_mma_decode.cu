@@ -7,7 +7,7 @@
 // A CTA works on 128-token tiles; all three matrix products of a tile run on the 5th-generation tensor
 // core (tcgen05.mma, accumulators in tensor memory), and a token row of the tile belongs to one thread
 // (tensor-memory lane = token), so neither RoPE nor the softmax weights need a shuffle.  The tile pipeline:
-//   2+2 gather warps : copy each token's ragged K / V coefficient row (16-byte cp.async, zero fill past the
+//   4+4 gather warps : copy each token's ragged K / V coefficient row (16-byte cp.async, zero fill past the
 //                      row's length) into K-major, unswizzled 128 x 128 operand tiles in shared memory; the
 //                      copy engine itself signals the tile's barrier when a lane's copies have landed;
 //   2 MMA threads    : per tile  (1) K = X . Bk          M=128 tokens, N=128, K=128 (A, B from shared memory)
@@ -43,12 +43,13 @@ constexpr int NCW = 8;                 // warps 0-3: RoPE stage, warps 4-7: soft
 // Service warps.  Warp w runs on SM sub-partition w % 4, next to RoPE warp w % 4 and softmax warp 4 + w % 4; the roles are
 // placed so that the sub-partitions of the two issuer threads do not also hold the (large) gather code: the
 // instruction caches are small and the issuers' instruction stream is the serial part of the pipeline.
-constexpr int W_KG0 = 8;               // K gather warps 8, 12 (64 tokens of the tile each)
+constexpr int W_KG0 = 8;               // K gather warps 8, 12 (32 tokens of the tile each; two more below)
 constexpr int W_VG0 = 9;               // V gather warps 9, 13
 constexpr int W_MMA = 10;              // tcgen05.mma issuer for products (1), (2); owns the tensor-memory allocation
 constexpr int W_ROT = 14;              // query rotator
 constexpr int W_MMA2 = 11;             // tcgen05.mma issuer for product (3)
-constexpr int NTHREADS = 16 * 32;      // 128 registers per thread
+constexpr int W_G2 = 16;               // gather warps 16, 17 (K) and 18, 19 (V): the second half of each side's four
+constexpr int NTHREADS = 20 * 32;      // at most 102 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
 constexpr int NBUF_A = 2;              // K operand tiles in shared memory
 constexpr int NBUF_T = 3;              // K accumulator buffers in tensor memory (held from product (1) to product (2))
@@ -311,8 +312,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   if (tid == 0) {
     sm.prefix[0] = 0;
     sm.abort_flag = 0;
-    for (int s = 0; s < NBUF_A; ++s) mbar_init(smem_u32(&sm.a_full[s]), 64);
-    for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), 64); mbar_init(smem_u32(&sm.v_free[s]), 1); }
+    for (int s = 0; s < NBUF_A; ++s) mbar_init(smem_u32(&sm.a_full[s]), ST_TOK);   // one arrival per gather lane
+    for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), ST_TOK); mbar_init(smem_u32(&sm.v_free[s]), 1); }
     for (int s = 0; s < NQ; ++s) mbar_init(smem_u32(&sm.q_full[s]), 1);
     for (int s = 0; s < NGROUP; ++s) {
       mbar_init(smem_u32(&sm.s_ready[s]), 1);
@@ -507,18 +508,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
   }
 
-  else if (warp == W_KG0 || warp == W_KG0 + 4 || warp == W_VG0 || warp == W_VG0 + 4) {
+  else if (warp == W_KG0 || warp == W_KG0 + 4 || warp == W_VG0 || warp == W_VG0 + 4 || warp >= W_G2) {
     // =========================== gather warps ===========================
-    // Lane l of gather warp j (of its side) owns tokens 64j + l and 64j + 32 + l of every tile: it stages their
-    // lengths and offsets (cp.async, PD tiles ahead, slots private to the lane) and copies each coefficient row
-    // into the operand tile, one 16-byte chunk per cp.async, chunk c of token t at c*2048 + t*16; chunks past
-    // the row's length are zero-filled (source size 0), so the tensor core always sees a full 128 x 128 tile.
-    const bool is_v = (warp & 3) == (W_VG0 & 3);
-    const int gw = (warp >> 2) & 1;
+    // Four warps per side; lane l of gather warp j owns token 32j + l of every tile: it stages the token's length
+    // and offset (cp.async, PD tiles ahead, slots private to the lane) and copies the coefficient row into the
+    // operand tile, one 16-byte chunk per cp.async, chunk c of token t at c*2048 + t*16; chunks past the row's
+    // length are zero-filled (source size 0), so the tensor core always sees a full 128 x 128 tile.
+    const bool is_v = warp >= W_G2 ? warp >= W_G2 + 2 : (warp & 3) == (W_VG0 & 3);
+    const int gw = warp >= W_G2 ? 2 + ((warp - W_G2) & 1) : (warp >> 2) & 1;
     const dkv_side& sd = is_v ? p.v : p.k;
     const int side = is_v ? 1 : 0;
     const int NB = is_v ? NBUF_V : NBUF_A;
-    const int tA = 64 * gw + lane;
+    const int t = 32 * gw + lane;
     RowInfo pre{row0, 0, 0, 0}, cur{row0, 0, 0, 0};
     int pre_end = -1, cur_end = -1;
     auto prefetch_meta = [&](int c) {   // no commit: the caller groups it with the tile's data copies
@@ -527,15 +528,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         if (u >= pre_end) { enter_row(pre, u); pre_end = sm.prefix[pre.row + 1]; }
         const int s0 = (u - pre.first_unit) * ST_TOK;
         int(*dst)[ST_TOK] = sm.meta[side][c % MSLOT];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int t = tA + 32 * k;
-          if (s0 + t < pre.tokens) {
-            cp_async4(smem_u32(&dst[0][t]), sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0 + t);
-            cp_async4(smem_u32(&dst[1][t]), sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0 + t);
-          } else {
-            dst[0][t] = 0; dst[1][t] = 0;
-          }
+        if (s0 + t < pre.tokens) {
+          cp_async4(smem_u32(&dst[0][t]), sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0 + t);
+          cp_async4(smem_u32(&dst[1][t]), sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0 + t);
+        } else {
+          dst[0][t] = 0; dst[1][t] = 0;
         }
       }
     };
@@ -546,20 +543,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const int u = u_begin + c;
       if (u >= cur_end) { enter_row(cur, u); cur_end = sm.prefix[cur.row + 1]; }
       int(*mt)[ST_TOK] = sm.meta[side][c % MSLOT];
-      int len[2], off[2];
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        len[k] = mt[0][tA + 32 * k];
-        off[k] = mt[1][tA + 32 * k];
-        if (((len[k] | off[k]) & 7) != 0 || len[k] < 0 || len[k] > R || off[k] < 0 || (int64_t)off[k] + len[k] > sd.flat_stride) {
-          set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
-          len[k] = 0;
-        }
+      int len = mt[0][t];
+      const int off = mt[1][t];
+      if (((len | off) & 7) != 0 || len < 0 || len > R || off < 0 || (int64_t)off + len > sd.flat_stride) {
+        set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
+        len = 0;
       }
       if (!is_v) {
-        const uint32_t m0 = __ballot_sync(0xffffffffu, len[0] > 0), m1 = __ballot_sync(0xffffffffu, len[1] > 0);
-        if (lane == 0) { sm.kvalid[c % KV_RING][2 * gw] = m0; sm.kvalid[c % KV_RING][2 * gw + 1] = m1; }
+        const uint32_t m = __ballot_sync(0xffffffffu, len > 0);
+        if (lane == 0) sm.kvalid[c % KV_RING][gw] = m;
       }
+      const unsigned char* row_src = reinterpret_cast<const unsigned char*>(
+          reinterpret_cast<const T*>(sd.flat) + (size_t)cur.arena * sd.flat_stride + (len > 0 ? off : 0));
       // the tensor core must be done with the tile that was in this buffer NB tiles ago
       // (K: product (1) of tile c-2 read this buffer; its completion is t_ready of that tile, ring of NBUF_T)
       if (c >= NB) {
@@ -567,17 +562,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         const uint32_t par = is_v ? (uint32_t)(((c / NBUF_V) - 1) & 1) : (uint32_t)(((c - NBUF_A) / NBUF_T) & 1);
         if (!mbar_wait(bar, par, abort_flag)) break;
       }
-      unsigned char* const tile = is_v ? sm.v_tile[buf] : sm.a_tile[buf];
+      const uint32_t dst = smem_u32(is_v ? sm.v_tile[buf] : sm.a_tile[buf]) + t * 16;
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const unsigned char* row_src = reinterpret_cast<const unsigned char*>(
-            reinterpret_cast<const T*>(sd.flat) + (size_t)cur.arena * sd.flat_stride + (len[k] > 0 ? off[k] : 0));
-        const uint32_t dst = smem_u32(tile) + (tA + 32 * k) * 16;
-#pragma unroll
-        for (int ch = 0; ch < 16; ++ch) {
-          // past the row's length the source size is 0: nothing is read from the (then meaningless) address
-          cp_async16_zfill(dst + ch * 2048, row_src + ch * 16, ch * 8 < len[k] ? 16 : 0);
-        }
+      for (int ch = 0; ch < 16; ++ch) {
+        // past the row's length the source size is 0: nothing is read from the (then meaningless) address
+        cp_async16_zfill(dst + ch * 2048, row_src + ch * 16, ch * 8 < len ? 16 : 0);
       }
       // The tile is handed over by the copy engine itself: each lane's arrival on the tile's barrier fires when
       // its copies have landed, so the warp neither waits for the data nor delays the hand-over until it comes
@@ -897,7 +886,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   if (project) {
     // out[head][d] = sum_r latent[head][r] * Bv[r][d]: one output element per thread
     const int h = tid >> 7, d = tid & 127;
-    if (h < G) {
+    if (h < HP && h < G) {
       const int b = p.batch_index ? p.batch_index[blockIdx.x] : blockIdx.x;
       const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * D + d;
       float acc0 = 0.f, acc1 = 0.f;

@@ -51,9 +51,9 @@ constexpr int W_MMA2 = 11;             // tcgen05.mma issuer for product (3)
 constexpr int W_G2 = 16;               // gather warps 16, 17 (K) and 18, 19 (V): the second half of each side's four
 constexpr int NTHREADS = 20 * 32;      // at most 102 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
-constexpr int NBUF_A = 2;              // K operand tiles in shared memory
+constexpr int NBUF_A = 3;              // K operand tiles in shared memory (on the critical ring: three in flight)
 constexpr int NBUF_T = 3;              // K accumulator buffers in tensor memory (held from product (1) to product (2))
-constexpr int NBUF_V = 3;              // V operand tiles
+constexpr int NBUF_V = 2;              // V operand tiles
 constexpr int NQ = 2;                  // rotated-query tiles
 constexpr int PD = 2;                  // prefetch distance of the gather warps' metadata (tiles)
 constexpr int MSLOT = PD + 1;          // metadata staging slots (private to the lane that fetched them)
@@ -597,8 +597,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       uint32_t rtp = 0, qtp = 0;   // ... and phases (ri / 3) & 1, (qi / 3) & 1
       uint32_t idle = 0;
       while (qi < n_stages) {
-        const int rb = ri & 1, qg = qi & 1;
-        const bool r_ok = mbar_probe(smem_u32(&sm.a_full[rb]), (uint32_t)((ri >> 1) & 1));
+        static_assert(NBUF_A == NBUF_T, "the K operand tiles and the K accumulators share ring index and phase");
+        const int rb = rt, qg = qi & 1;
+        const bool r_ok = mbar_probe(smem_u32(&sm.a_full[rb]), rtp);
         const bool k_ok = mbar_probe(smem_u32(&sm.kp_ready[qt]), qtp);
         const bool q_ok = mbar_probe(smem_u32(&sm.q_full[qg]), (uint32_t)((qi >> 1) & 1)) &&
                           (qi < 2 || mbar_probe(smem_u32(&sm.p_ready[qg]), (uint32_t)(((qi >> 1) - 1) & 1)));   // score tile read out

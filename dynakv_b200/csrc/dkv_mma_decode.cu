@@ -83,8 +83,8 @@ struct SmemLayout {
   alignas(16) float rs_buf[4][ST_TOK];                      // K-RMSNorm: 1/rms of the tokens of the last four tiles
   alignas(16) float knorm_w[D];
   uint32_t kvalid[KV_RING][4];                              // bit l of word w: token 32w + l of the tile has a K row
-  alignas(8) unsigned long long a_full[NBUF_A];    // K operand tile written (2 gather warps)
-  alignas(8) unsigned long long v_full[NBUF_V];    // V operand tile written (2 gather warps)
+  alignas(8) unsigned long long a_full[NBUF_A];    // K operand tile written (128 gather lanes)
+  alignas(8) unsigned long long v_full[NBUF_V];    // V operand tile written (128 gather lanes)
   alignas(8) unsigned long long v_free[NBUF_V];    // product (3) done with it (commit)
   alignas(8) unsigned long long q_full[NQ];        // rotated queries written (rotator)
   alignas(8) unsigned long long t_ready[NBUF_T];   // K accumulator written (commit)

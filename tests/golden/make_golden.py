@@ -255,7 +255,9 @@ def gate_fixture(name, seed, n_rows, d):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
+    ref = sys.argv[1]
     sys.path.insert(0, os.path.join(ref, "src"))
     torch.manual_seed(0)
     # per-KV-head layout, lengths multiples of 8 (the measured configurations' form)

@@ -43,7 +43,8 @@ enum {
 enum {
   DKV_ST_OVERFLOW = 1,   /* an append/pack would have written past flat capacity or seq capacity; skipped */
   DKV_ST_BAD_LENGTH = 2, /* a length was negative, above max_dim, or not a multiple of the declared step */
-  DKV_ST_EMPTY_ROW = 4   /* attention over a row with no valid token; output written as zeros */
+  DKV_ST_EMPTY_ROW = 4,  /* attention over a row with no valid token; output written as zeros */
+  DKV_ST_TIMEOUT = 8     /* a bounded wait inside a kernel ran out; that call's output is not valid */
 };
 
 /* One side (K or V) of one layer's ragged cache.

@@ -4,24 +4,28 @@
 //   * the long-cache split path: a persistent grid that partitions each KV head's token space
 //     evenly over CTAs and writes (m, l, latent accumulator) partials, merged by a combine kernel.
 //
-// A CTA works on 128-token tiles.  Per tile:
-//   K gather (4 warps)  : each lane copies its token's ragged K coefficient row (16-byte cp.async, zero fill past
-//                         the row's length) into a K-major 128 x 128 operand tile in shared memory;
-//   service warp        : one lane issues the K reconstruction  K = X . Bk  (tcgen05.mma, M = 128 tokens, N = 128,
-//                         K = 128, accumulator in tensor memory); the warp then publishes the rotated queries
-//                         Q~ = scale . R(-s0) q for the tile's base position s0 as mma.sync A fragments, so K is
-//                         rotated only by the in-tile offset 0..127;
-//   V gather (4 warps)  : each lane copies its token's V coefficient row into a row-major tile (one token per
-//                         272-byte row), zero-filled only up to the longest row of its 16-token group;
-//   compute (8 warps)   : warp w owns tokens 16w'..16w'+15 of every tile.  It reads their K rows from tensor
-//                         memory in the mma.sync fragment layout (tcgen05.ld.16x256b), applies [RMSNorm and] RoPE
-//                         in fp32 registers (the cos/sin of its in-tile offsets stay in registers), and feeds K'
-//                         straight into mma.sync as the B operand of  S^T = Q~ . K'^T  (no round trip through
-//                         tensor or shared memory).  Online softmax is private to the warp (own running maximum,
-//                         own sum); P^T is the A operand of  O += P^T . XV  (mma.sync, B via ldmatrix.trans from the
-//                         V tile, only as many latent columns as the group's longest V row), with O[4 heads x 128
-//                         latent] in registers.  At the end of a batch row the eight warps merge their partials.
-// The compute warps raise their register allowance (setmaxnreg) from what the gather and service warps release.
+// A CTA works on 128-token tiles; all three matrix products of a tile run on the 5th-generation tensor
+// core (tcgen05.mma, accumulators in tensor memory), and a token row of the tile belongs to one thread
+// (tensor-memory lane = token), so neither RoPE nor the softmax weights need a shuffle.  The tile pipeline:
+//   4+4 gather warps : copy each token's ragged K / V coefficient row (16-byte cp.async, zero fill past the
+//                      row's length) into K-major, unswizzled 128 x 128 operand tiles in shared memory; the
+//                      copy engine itself signals the tile's barrier when a lane's copies have landed;
+//   2 MMA threads    : per tile  (1) K = X . Bk          M=128 tokens, N=128, K=128 (A, B from shared memory)
+//                                (2) S = K' . Q~^T       M=128 tokens, N=16,  K=128 (A = K' in tensor memory)
+//                                (3) O^T += XV^T . P     M=128 latent, N=16,  K=128 tokens (accumulates per row);
+//                      one thread issues (1) and (2) from an event loop over barrier probes, another issues (3);
+//                      completion of each product is signalled by tcgen05.commit on mbarriers;
+//   1 rotator warp   : Q~ = scale . R(-s0) q for the tile's base position s0 (the B operand of (2)), so K is
+//                      rotated only by the in-tile offset 0..127;
+//   4 RoPE warps     : a thread reads its token's K row from one of three accumulator buffers (tcgen05.ld.32x32b),
+//                      applies [RMSNorm and] RoPE in fp32 with its 64 (cos, sin) pairs, which also live in tensor
+//                      memory (fp16 pairs; they depend on the lane only), and writes K' back in place as packed
+//                      16-bit pairs (tcgen05.st) for product (2);
+//   4 softmax warps  : a thread reads its token's four scores, takes p = exp2(s - m_ref) against a reference
+//                      maximum shared by the four warps, which is only raised (with a rescale of O in tensor
+//                      memory) when a tile exceeds it by more than 2^8, and stores P for product (3); these
+//                      warps follow the batch rows and write each row's partial (split) or projected (fused)
+//                      result.
 //
 // Reference math: src/dynakv/kernels/fused.py:28-142 (fused), two_stage.py:52-157,211-281 (two-stage;
 // the latent-space V accumulation with one up-projection at the end is two_stage.py:261-277).
@@ -34,73 +38,71 @@
 namespace dkv {
 
 constexpr int D = 128;
-constexpr int N_CW = 8;                // compute warps 0..7 (warpgroups 0 and 1)
-constexpr int W_KG0 = 8;               // K gather warps 8..11 (warpgroup 2)
-constexpr int W_VG0 = 12;              // V gather warps 12..15 (warpgroup 3)
-constexpr int NTHREADS = 16 * 32;
-constexpr int REGS_COMPUTE = 200;      // per-thread register allowances after the roles split (setmaxnreg):
-constexpr int REGS_OTHER = 56;         // 8 x 32 x 200 + 8 x 32 x 56 = 64 K registers
+constexpr int NGROUP = 2;              // score tiles / P tiles in flight (tile parity)
+constexpr int NCW = 8;                 // warps 0-3: RoPE stage, warps 4-7: softmax stage
+// Service warps.  Warp w runs on SM sub-partition w % 4, next to RoPE warp w % 4 and softmax warp 4 + w % 4; the roles are
+// placed so that the sub-partitions of the two issuer threads do not also hold the (large) gather code: the
+// instruction caches are small and the issuers' instruction stream is the serial part of the pipeline.
+constexpr int W_KG0 = 8;               // K gather warps 8, 12 (32 tokens of the tile each; two more below)
+constexpr int W_VG0 = 9;               // V gather warps 9, 13
+constexpr int W_MMA = 10;              // tcgen05.mma issuer for products (1), (2); owns the tensor-memory allocation
+constexpr int W_ROT = 14;              // query rotator
+constexpr int W_MMA2 = 11;             // tcgen05.mma issuer for product (3)
+constexpr int W_G2 = 16;               // gather warps 16, 17 (K) and 18, 19 (V): the second half of each side's four
+constexpr int NTHREADS = 20 * 32;      // at most 102 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
-constexpr int NRING = 3;               // K operand tiles = K accumulators = rotated-query slots (one ring)
-constexpr int NBUF_V = 2;              // V tiles
+constexpr int NBUF_A = 3;              // K operand tiles in shared memory (on the critical ring: three in flight)
+constexpr int NBUF_T = 3;              // K accumulator buffers in tensor memory (held from product (1) to product (2))
+constexpr int NBUF_V = 2;              // V operand tiles
+constexpr int NQ = 2;                  // rotated-query tiles
 constexpr int PD = 2;                  // prefetch distance of the gather warps' metadata (tiles)
 constexpr int MSLOT = PD + 1;          // metadata staging slots (private to the lane that fetched them)
-// Token-validity masks: the K gather writes tile c's mask after product (1) of tile c - NRING has completed, which
-// needs the accumulator of tile c - 2 NRING released, i.e. every compute warp has started (not finished) tile
-// c - 2 NRING.  So masks of tiles c - 2 NRING .. c are live at once.
-constexpr int KV_RING = 8;
-static_assert(KV_RING > 2 * NRING, "validity-mask ring must cover the K gather's lead over the compute warps");
-constexpr int TILE_BYTES = ST_TOK * 128 * 2;   // K operand tile: 128 tokens x 128 coefficients, chunk-major
-constexpr int V_PITCH = 272;                   // bytes between token rows of a V tile (256 + 16: ldmatrix bank spread)
-constexpr int V_TILE_BYTES = ST_TOK * V_PITCH;
+constexpr int KV_RING = 8;             // tiles of token-validity masks kept
+// 1/rms ring: a RoPE write for tile c only implies that the softmax warps have finished tile c-5 (product (1) of c
+// needs product (2) of c-3 issued, which needs the P tile of c-5), so tiles c-4 .. c may be unread
+constexpr int RS_RING = 8;
+static_assert(RS_RING >= 5, "1/rms ring must cover the RoPE warps' lead over the softmax warps");
+constexpr int TILE_BYTES = ST_TOK * 128 * 2;   // 128 tokens x 128 coefficients, chunk-major
+constexpr int Q_LBO = 272;             // byte distance of the 8-dim chunks of the rotated-query tile (bank spread)
+constexpr int Q_TILE_BYTES = 16 * Q_LBO;
 constexpr int HP = 4;                  // query heads per KV head supported by this kernel
 constexpr int MAX_BATCH = 1024;
 constexpr int PART_STRIDE = 2 + 128;   // floats per (head) partial record: m, l, latent[128]
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr float M_SLACK = 8.f;         // a tile may exceed a warp's running maximum by 2^8 before O is rescaled
-constexpr uint32_t TMEM_COLS = 512;    // three 128-column K accumulators (allocation sizes are powers of two)
+constexpr float M_SLACK = 8.f;         // a tile may exceed the reference maximum by 2^8 before O is rescaled
+// tensor-memory columns (32-bit cells): three K accumulators, the RoPE table (fp16 pairs), two score tiles, one O
+// accumulator
+constexpr uint32_t TM_K = 0, TM_TRIG = 384, TM_S = 448, TM_O = 480, TMEM_COLS = 512;
 
 struct SmemLayout {
-  alignas(1024) unsigned char a_tile[NRING][TILE_BYTES];    // chunk c (8 coefficients) of token t at c*2048 + t*16
+  alignas(1024) unsigned char a_tile[NBUF_A][TILE_BYTES];   // chunk c (8 coefficients) of token t at c*2048 + t*16
+  alignas(1024) unsigned char v_tile[NBUF_V][TILE_BYTES];   // same layout; [NBUF_V-1] stages the RoPE table in the prologue
   alignas(1024) unsigned char basis[128 * 256];             // Bk[r][d] at (r/8)*2048 + (d/8)*128 + (r%8)*16 + (d%8)*2
-  alignas(128) unsigned char v_tile[NBUF_V][V_TILE_BYTES];  // latent chunk c of token t at t*272 + c*16
-  alignas(16) uint32_t qfrag[NRING][4][32][4];              // [slot][i][lane]{a0a1(ks=i), a4a5(ks=i), a0a1(ks=4+i), a4a5(ks=4+i)}
-  alignas(16) float part_o[N_CW / 2][HP][128];              // row end: latent accumulators of a warp pair (w, w + 4)
-  alignas(16) float part_m[N_CW / 2][HP];
-  alignas(16) float part_l[N_CW / 2][HP];
+  alignas(128) unsigned char qrot[NQ][Q_TILE_BYTES];        // Q~[n][d] at (d/8)*272 + (n/8)*128 + (n%8)*16 + (d%8)*2
+  alignas(128) unsigned char p_tile[NGROUP][ST_TOK * 16];   // P[t][n < 8] at t*16
   alignas(16) int meta[2][MSLOT][2][ST_TOK];                // [K|V][slot][lens|offs][token]
   alignas(16) float lat[HP][128];                           // fused path: normalised latent result of a row
+  alignas(16) float tmax[2][4][4];                          // [tile parity][warp][head]
+  alignas(16) float lsum[4][4];                             // [warp][head]
+  alignas(16) float rs_buf[RS_RING][ST_TOK];                // K-RMSNorm: 1/rms of the tokens of the last tiles
   alignas(16) float knorm_w[D];
   uint32_t kvalid[KV_RING][4];                              // bit l of word w: token 32w + l of the tile has a K row
-  int vfill[NBUF_V][8];                                     // 16-latent column pairs filled for each 16-token group
-  alignas(8) unsigned long long a_full[NRING];     // K operand tile written (128 copy arrivals + 4 warp arrivals)
-  alignas(8) unsigned long long t_ready[NRING];    // K accumulator written, operand tile free (commit)
-  alignas(8) unsigned long long acc_free[NRING];   // accumulator and rotated-query slot read out (8 compute warps)
-  alignas(8) unsigned long long q_full[NRING];     // rotated queries written (4 V gather warps, one head each)
-  alignas(8) unsigned long long v_full[NBUF_V];    // V tile written (128 copy arrivals + 4 warp arrivals)
-  alignas(8) unsigned long long v_free[NBUF_V];    // V tile read (8 compute warps)
-  alignas(8) unsigned long long row_sync;          // row-end rendezvous of the 8 compute warps
+  alignas(8) unsigned long long a_full[NBUF_A];    // K operand tile written (128 gather lanes)
+  alignas(8) unsigned long long v_full[NBUF_V];    // V operand tile written (128 gather lanes)
+  alignas(8) unsigned long long v_free[NBUF_V];    // product (3) done with it (commit)
+  alignas(8) unsigned long long q_full[NQ];        // rotated queries written (rotator)
+  alignas(8) unsigned long long t_ready[NBUF_T];   // K accumulator written (commit)
+  alignas(8) unsigned long long kp_ready[NBUF_T];  // K' written back to tensor memory (4 RoPE warps)
+  alignas(8) unsigned long long s_ready[NGROUP];   // scores written (commit)
+  alignas(8) unsigned long long p_ready[NGROUP];   // P tile written (4 token warps)
+  alignas(8) unsigned long long pv_done[NGROUP];   // product (3) done: O updated, P tile free (commit)
+  alignas(8) unsigned long long grp_sync;          // per-tile rendezvous of the 4 softmax warps (tile maxima)
   int prefix[MAX_BATCH + 1];
   int abort_flag;
   uint32_t tmem_base;
 };
 static_assert(sizeof(SmemLayout) <= 227 * 1024, "shared memory budget");
-static_assert(ST_TOK * 64 * 8 <= NRING * TILE_BYTES, "RoPE staging table must fit in the K operand tiles");
-
-#ifdef DKV_TRACE
-// Debug builds only: per-role clock stamps of the first tiles of CTA (0, 0).
-constexpr int TR_TILES = 96, TR_ROLES = 6, TR_PTS = 6;
-__device__ long long g_trace[TR_ROLES][TR_TILES][TR_PTS];
-__device__ unsigned int g_qdbg[2][64][32][4];
-__device__ float g_pdbg[64][9][4][2];   // [cta][warp 0..7 | 8 = merged][head]{m, l}
-#define PDBG(w, h, m, l) do { const int cta__ = blockIdx.y * gridDim.x + blockIdx.x; if (cta__ < 64) { g_pdbg[cta__][w][h][0] = (m); g_pdbg[cta__][w][h][1] = (l); } } while (0)
-#define QDBG(which, c, h, val) do { const int cta__ = blockIdx.y * gridDim.x + blockIdx.x; if (cta__ < 64 && (c) < 32) g_qdbg[which][cta__][c][h] = (val); } while (0)
-#define TRACE(role, c, pt) do { if (blockIdx.x == 1 && blockIdx.y == 0 && (c) < TR_TILES && (threadIdx.x & 31) == 0) g_trace[role][c][pt] = clock64(); } while (0)
-#else
-#define TRACE(role, c, pt) do { } while (0)
-#define QDBG(which, c, h, val) do { } while (0)
-#define PDBG(w, h, m, l) do { } while (0)
-#endif
+static_assert(ST_TOK * 65 * 4 <= NBUF_V * TILE_BYTES, "RoPE staging table must fit in the V tiles");
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -121,11 +123,11 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait for a whole warp: returns false (and raises the CTA's abort flag) instead of spinning forever.
-// Only lane 0 polls the barrier -- hundreds of threads polling would compete with the async copies for the
-// shared-memory barrier unit.  Once it has seen the phase complete, every lane tests the barrier once itself:
-// the acquire of lane 0 orders nothing for the other lanes, and without one of their own their later
-// shared-memory loads may be scheduled ahead of the wait.
+// Every lane tests the barrier itself (one instruction for the warp), so each has its own acquire: with a single
+// polling lane the other lanes' later shared-memory loads are not ordered behind the wait and can be scheduled
+// ahead of it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#ifdef DKV_POLL_LANE0
   int ok = 0;
   if ((threadIdx.x & 31) == 0) {
     for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
@@ -138,6 +140,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (ok) (void)mbar_test(bar, parity);
   __syncwarp();
   return ok != 0;
+#else
+  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+    if (mbar_test(bar, parity)) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+#endif
+}
+// Non-blocking probe of a barrier phase.
+__device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// The same for a single thread (the tensor-core issuers run on one lane).
+__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+    if (mbar_test(bar, parity)) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
 }
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
@@ -153,14 +182,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void set_max_regs_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void set_max_regs_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 // tcgen05 (5th generation tensor core) helpers ---------------------------------------------------------
 // Shared-memory matrix descriptor, no swizzle: start address, leading and stride byte offsets in 16-byte
@@ -179,32 +200,65 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// tcgen05.mma with the A operand in tensor memory (16-bit pairs packed in 32-bit cells, lane = row)
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Tensor-memory load in the mma.sync accumulator layout (16 lanes x 256 bits, twice = 16 columns): thread
-// (g = lane / 4, t = lane % 4) receives, for each 8-column block k = 0, 1,
-//   r[4k + 0], r[4k + 1] = lane (base + g),     columns 8k + 2t, 8k + 2t + 1
-//   r[4k + 2], r[4k + 3] = lane (base + g + 8), columns 8k + 2t, 8k + 2t + 1.
-// Two such loads (a 16-column block and its rotation partners 64 columns up) and the wait share one statement,
-// so no result register can be touched before the data has landed.
-__device__ __forceinline__ void tmem_ld_frag2(float (&lo)[8], float (&hi)[8], uint32_t a_lo, uint32_t a_hi) {
+// Thread-per-lane tensor-memory access (32x32b shapes): thread i of the warp addresses lane (base lane + i),
+// register k holds column (base column + k).  Every load carries its wait in the same statement, so no
+// result register can be touched before the data has landed.
+// One RoPE chunk: 8 K values of dims j0..j0+7, their rotation partners (dims +64) and the 8 table cells (fp16 pairs).
+__device__ __forceinline__ void tmem_ld_rope_chunk(float (&lo)[8], float (&hi)[8], uint32_t (&tg)[8], uint32_t a_lo,
+                                                   uint32_t a_hi, uint32_t a_tg) {
   uint32_t r[16];
   asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%16];\n"
-      "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%8,%9,%10,%11,%12,%13,%14,%15}, [%17];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%24];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%8,%9,%10,%11,%12,%13,%14,%15}, [%25];\n"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%16,%17,%18,%19,%20,%21,%22,%23}, [%26];\n"
       "tcgen05.wait::ld.sync.aligned;"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(a_lo), "r"(a_hi)
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(tg[0]), "=r"(tg[1]), "=r"(tg[2]), "=r"(tg[3]), "=r"(tg[4]), "=r"(tg[5]), "=r"(tg[6]), "=r"(tg[7])
+      : "r"(a_lo), "r"(a_hi), "r"(a_tg)
       : "memory");
 #pragma unroll
   for (int i = 0; i < 8; ++i) { lo[i] = __uint_as_float(r[i]); hi[i] = __uint_as_float(r[8 + i]); }
 }
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
+__device__ __forceinline__ void tmem_ld4(float (&v)[4], uint32_t addr) {
+  uint32_t r[4];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];\ntcgen05.wait::ld.sync.aligned;"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_st4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const float (&v)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+                 "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+                 "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+                 "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+                 "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+               : "memory");
+}
+
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(4 * 32) : "memory"); }   // the 4 softmax warps
+
+// order-preserving map float -> int (and back: the map is its own inverse), for redux.sync
+__device__ __forceinline__ int float_key(float f) {
+  const int i = __float_as_int(f);
+  return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
+__device__ __forceinline__ float warp_max_redux(float v) { return key_float(__reduce_max_sync(0xffffffffu, float_key(v))); }
 
 template <typename T>
 struct Pack;
@@ -222,28 +276,6 @@ struct Pack<__half> {
     return *reinterpret_cast<uint32_t*>(&v);
   }
 };
-
-// mma.sync m16n8k16 with fp32 accumulation.  Only rows 0..7 of A are ever non-zero here (rows = query heads,
-// four of them real), so a1 = a3 = 0 and the accumulator rows 8..15 (d2, d3) are discarded.
-template <typename T>
-__device__ __forceinline__ void mma_rows8(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-  float x2, x3;
-  if (std::is_same<T, __nv_bfloat16>::value) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
-                 : "+f"(d0), "+f"(d1), "=f"(x2), "=f"(x3)
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
-  } else {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
-                 : "+f"(d0), "+f"(d1), "=f"(x2), "=f"(x3)
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
-  }
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr)
-               : "memory");
-}
 
 // --------------------------------------------------------------- work partition
 // Token space of one KV head: batch rows back to back, each rounded up to whole 128-token tiles.
@@ -264,50 +296,8 @@ struct WsHeader {  // start of the split workspace, written by the split kernel,
 };
 __host__ __device__ constexpr size_t ws_header_bytes() { return (sizeof(WsHeader) + 255) / 256 * 256; }
 
-// RoPE of four (dim j, dim j + 64) pairs of two tokens, then the score products that consume them.
-//   lo / hi : a 16-column block of the K accumulator (column blocks cb = 2 I, 2 I + 1 of the 16 blocks of 8) and
-//             its partners 64 columns up, in the tcgen05.ld.16x256b layout above
-//   ct / st : cos and sin of (token offset) * f_j for this thread's two tokens and its 16 pairs
-// K' goes straight into mma.sync B fragments: the k-step of dims 16 I .. 16 I + 15 takes block 2 I (b0) and
-// 2 I + 1 (b1), and the partners form k-step 4 + I.  sa / sb accumulate the low / high half of the dot product
-// for token block e (0: lanes g, 1: lanes g + 8).
-template <typename T, bool KNORM, int I>
-__device__ __forceinline__ void rope_scores(const float (&lo)[8], const float (&hi)[8], const float2 (&ct)[2][8],
-                                            const float2 (&st)[2][8], const uint32_t* qf_lane, const float* knorm_w,
-                                            int t, float (&ss)[2], float (&sa)[2][2], float (&sb)[2][2]) {
-  uint32_t blo[2][2], bhi[2][2];       // [token block e][b0 | b1]
-#pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    const int cb = 2 * I + k;
-    float2 wl = make_float2(1.f, 1.f), wh = make_float2(1.f, 1.f);
-    if (KNORM) {
-      wl = *reinterpret_cast<const float2*>(knorm_w + 8 * cb + 2 * t);
-      wh = *reinterpret_cast<const float2*>(knorm_w + 64 + 8 * cb + 2 * t);
-    }
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      float2 L = make_float2(lo[4 * k + 2 * e], lo[4 * k + 2 * e + 1]);
-      float2 H = make_float2(hi[4 * k + 2 * e], hi[4 * k + 2 * e + 1]);
-      if (KNORM) {
-        ss[e] = fmaf(L.x, L.x, fmaf(L.y, L.y, fmaf(H.x, H.x, fmaf(H.y, H.y, ss[e]))));
-        L = __fmul2_rn(L, wl);
-        H = __fmul2_rn(H, wh);
-      }
-      const float2 C = ct[e][cb], S = st[e][cb];
-      const float2 nH = make_float2(-H.x, -H.y);
-      const float2 lo2 = __ffma2_rn(nH, S, __fmul2_rn(L, C));
-      const float2 hi2 = __ffma2_rn(L, S, __fmul2_rn(H, C));
-      blo[e][k] = Pack<T>::two(lo2.x, lo2.y);
-      bhi[e][k] = Pack<T>::two(hi2.x, hi2.y);
-    }
-  }
-  const uint4 qa = *reinterpret_cast<const uint4*>(qf_lane + I * 32 * 4);
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    mma_rows8<T>(sa[e][0], sa[e][1], qa.x, qa.y, blo[e][0], blo[e][1]);
-    mma_rows8<T>(sb[e][0], sb[e][1], qa.z, qa.w, bhi[e][0], bhi[e][1]);
-  }
-}
+// per-row facts cached by the warps that walk the tile sequence
+struct RowInfo { int row, arena, tokens, first_unit; };
 
 // ------------------------------------------------------------------ the kernel
 template <typename T, bool FUSED, bool KNORM>
@@ -325,18 +315,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
 
   // ---- prologue A: everything that does not depend on the kernel before this one -----------------------
   // (programmatic dependent launch: this part overlaps the tail of the preceding kernel in the stream, which
-  // may still be appending this step's token; only the bases and the K-norm weight are read here)
+  // may still be appending this step's token; only the K basis is read here)
   if (tid == 0) {
     sm.prefix[0] = 0;
     sm.abort_flag = 0;
-    for (int s = 0; s < NRING; ++s) {
-      mbar_init(smem_u32(&sm.a_full[s]), ST_TOK + 4);   // one arrival per gather lane's copies + one per gather warp
-      mbar_init(smem_u32(&sm.t_ready[s]), 1);
-      mbar_init(smem_u32(&sm.acc_free[s]), N_CW);
-      mbar_init(smem_u32(&sm.q_full[s]), 4);
+    for (int s = 0; s < NBUF_A; ++s) mbar_init(smem_u32(&sm.a_full[s]), ST_TOK);   // one arrival per gather lane
+    for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), ST_TOK); mbar_init(smem_u32(&sm.v_free[s]), 1); }
+    for (int s = 0; s < NQ; ++s) mbar_init(smem_u32(&sm.q_full[s]), 1);
+    for (int s = 0; s < NGROUP; ++s) {
+      mbar_init(smem_u32(&sm.s_ready[s]), 1);
+      mbar_init(smem_u32(&sm.p_ready[s]), 4);
+      mbar_init(smem_u32(&sm.pv_done[s]), 1);
     }
-    for (int s = 0; s < NBUF_V; ++s) { mbar_init(smem_u32(&sm.v_full[s]), ST_TOK + 4); mbar_init(smem_u32(&sm.v_free[s]), N_CW); }
-    mbar_init(smem_u32(&sm.row_sync), N_CW);
+    for (int s = 0; s < NBUF_T; ++s) { mbar_init(smem_u32(&sm.t_ready[s]), 1); mbar_init(smem_u32(&sm.kp_ready[s]), 4); }
+    mbar_init(smem_u32(&sm.grp_sync), 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   {
@@ -349,35 +341,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       if (r < R) v = src[r * 16 + c];
       *reinterpret_cast<uint4*>(sm.basis + (r >> 3) * 2048 + c * 128 + (r & 7) * 16) = v;
     }
-    if (warp == W_KG0) {
+    if (warp == W_MMA) {
       asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
                    "r"(TMEM_COLS));
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
     }
-    // RoPE table for the in-tile offsets t = 0..127: angle = t * f_j, f_j = exp(-(2j/D) ln theta), staged in the
-    // (not yet used) K operand tiles as fp32 cos[t][j] and, 32 KB further, sin[t][j].  NTHREADS is a multiple of
-    // 64, so a thread keeps one j and steps t by NTHREADS/64: one exact sincos, then a fixed-angle rotation per step.
+    // RoPE table for the in-tile offsets t = 0..127: angle = t * f_j, f_j = exp(-(2j/D) ln theta), staged as
+    // 16-bit cells tr[t][4*(j/2) + (j&1)] = cos, [.. + 2] = sin (row pitch 130 cells = 65 words): per two pairs one
+    // word of cosines and one of sines, kept in fp16 (2^-11 absolute, below the 16-bit rounding of K').
+    // NTHREADS is a multiple of 64, so a thread keeps one j and steps t by NTHREADS/64: one exact sincos, then a
+    // fixed-angle rotation per step.
     static_assert(NTHREADS % 64 == 0, "trig table fill assumes a fixed j per thread");
     constexpr int TSTEP = NTHREADS / 64;
-    float* tc = reinterpret_cast<float*>(sm.a_tile[0]);
-    float* ts = tc + ST_TOK * 64;
+    __half* tr = reinterpret_cast<__half*>(sm.v_tile[0]);   // spans the (contiguous) V tiles until the pipeline starts
     const int j = tid & 63;
     const float f = expf(-((float)(2 * j) / (float)D) * log_theta);
     float sn, cs, ds, dc;
     sincosf((float)(tid >> 6) * f, &sn, &cs);
     sincosf((float)TSTEP * f, &ds, &dc);
     for (int t = tid >> 6; t < ST_TOK; t += TSTEP) {
-      tc[t * 64 + j] = cs;
-      ts[t * 64 + j] = sn;
+      const int idx = t * 130 + 4 * (j >> 1) + (j & 1);
+      tr[idx] = __float2half_rn(cs);
+      tr[idx + 2] = __float2half_rn(sn);
       const float c2 = cs * dc - sn * ds, s2 = sn * dc + cs * ds;
       cs = c2; sn = s2;
     }
-    if (KNORM && tid < D) sm.knorm_w[tid] = p.k_norm_weight[tid];
-    for (int e = tid; e < NRING * 4 * 32 * 4; e += NTHREADS) (&sm.qfrag[0][0][0][0])[e] = 0u;   // rows no V warp ever writes
+    for (int e = tid; e < NQ * Q_TILE_BYTES / 4; e += NTHREADS) reinterpret_cast<uint32_t*>(sm.qrot)[e] = 0u;   // rows the rotator never writes
   }
 
   // ---- prologue B: partition table (cache lengths: written by the kernel before this one) ----------------
   pdl_wait();
+  if (KNORM && tid >= 128 && tid < 128 + D) sm.knorm_w[tid - 128] = p.k_norm_weight[tid - 128];   // may be produced by the kernel before
   if (warp == 0) {
     // inclusive scan of the per-row tile counts, 32 rows at a time
     int carry = 0;
@@ -397,10 +391,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
-
-  const int cq = warp & 3, chf = (warp >> 2) & 1;          // tensor-memory lane quarter / 16-lane half of a compute warp
-  const int fg = lane >> 2, ft = lane & 3;                 // mma.sync fragment coordinates
-  const int tok0 = 32 * cq + 16 * chf;                     // first of a compute warp's 16 tokens in every tile
+  if (warp < 4) {
+    // the table row of this thread's in-tile offset goes to its tensor-memory lane
+    const float* tr = reinterpret_cast<const float*>(sm.v_tile[0]) + tid * 65;   // 64 packed words of this row
+    const uint32_t dst = tmem_base + ((uint32_t)(32 * warp) << 16) + TM_TRIG;
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = tr[16 * blk + i];
+      tmem_st16(dst + 16 * blk, v);
+    }
+    tmem_wait_st();
+  }
+  proxy_fence_async();     // the basis was written with ordinary stores and is read by the tensor core
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   const int total_units = sm.prefix[p.batch];
   int u_begin, u_end;
@@ -440,439 +447,448 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
     row0 = FUSED ? (int)blockIdx.x : lo;
   }
-  // ---- the roles split; registers move from the gather / service warpgroups to the compute warpgroups ----
-  // (each side finishes the set-up inside its own branch, so that nothing the compute warps keep in their
-  // enlarged register file is live in code the other warps share)
-  if (warp < N_CW) {
-    float2 ct[2][8], st[2][8];
-    set_max_regs_inc<REGS_COMPUTE>();
-    // cos / sin of this thread's two in-tile token offsets (tensor-memory lanes tok0 + g and tok0 + g + 8) times
-    // its sixteen frequencies j = 8 cb + 2 t, + 1 (cb = 0..7), kept in registers for the whole kernel
-    const float* tc = reinterpret_cast<const float*>(sm.a_tile[0]);
-    const float* ts = tc + ST_TOK * 64;
-#pragma unroll
-    for (int e = 0; e < 2; ++e)
-#pragma unroll
-      for (int cb = 0; cb < 8; ++cb) {
-        ct[e][cb] = *reinterpret_cast<const float2*>(tc + (tok0 + fg + 8 * e) * 64 + 8 * cb + 2 * ft);
-        st[e][cb] = *reinterpret_cast<const float2*>(ts + (tok0 + fg + 8 * e) * 64 + 8 * cb + 2 * ft);
-      }
-    proxy_fence_async();     // every thread wrote part of the basis with ordinary stores; the tensor core reads it
-    tc_fence_before();
-    __syncthreads();         // the staging table has been read: the gather may now overwrite the K operand tiles
-    tc_fence_after();
-    if (n_stages > 0) {
-    // ============================= compute warps =============================
-    const uint32_t lane_addr = tmem_base + ((uint32_t)tok0 << 16);
-    const uint32_t* const qf_lane = &sm.qfrag[0][0][lane][0];
-    const uint32_t v_lane = smem_u32(sm.v_tile[0]) + (uint32_t)(tok0 + ((lane >> 3) & 1) * 8 + (lane & 7)) * V_PITCH + (lane >> 4) * 16;
-    const int vgrp = 2 * cq + chf;               // this warp's 16-token group
-    const bool head_lane = fg < HP;              // lanes 0..15 hold the four real heads' scores
-    uint32_t row_phase = 0;
+  auto enter_row = [&](RowInfo& ri, int u) {
+    while (u >= sm.prefix[ri.row + 1]) ++ri.row;
+    const int b = p.batch_index ? p.batch_index[ri.row] : ri.row;
+    ri.arena = b * p.arenas_per_batch + g;
+    ri.tokens = row_tokens(p, ri.row);
+    ri.first_unit = sm.prefix[ri.row];
+  };
 
+  if (n_stages <= 0) {
+    // nothing to do for this CTA (fewer tiles than CTAs, or an empty row): straight to the epilogue
+  }
+  else if (warp == W_ROT) {
+    // =========================== query rotator warp ===========================
+    // For every tile (base position s0) it publishes Q~ = scale * R(-s0) q for the group's heads as rows 0..3 of
+    // the B operand of product (2), so that q~ . R(t) k = q . R(s0 + t) k with the in-tile offset t = 0..127
+    // (the rotation the token threads apply).  Rows 4..15 stay zero.  Lane l owns the pairs j = 2l, 2l+1.
+    const float f0 = expf(-((float)(4 * lane) / (float)D) * log_theta);
+    const float f1 = expf(-((float)(4 * lane + 2) / (float)D) * log_theta);
+    float cd0, sd0, cd1, sd1;     // rotation by one tile
+    sincosf((float)ST_TOK * f0, &sd0, &cd0);
+    sincosf((float)ST_TOK * f1, &sd1, &cd1);
+    const float qscale = rsqrtf((float)D) * 1.4426950408889634f;  // softmax scale and log2(e) folded into q
+    float a0[HP], b0[HP], a1[HP], b1[HP];   // (q~_j, q~_{j+64}) for j = 2l and j = 2l+1
     int row = row0;
-    bool dead = false;
-    while (row < p.batch && sm.prefix[row] < u_end) {
-      const int c_lo = max(sm.prefix[row], u_begin) - u_begin;     // tiles of this row in this CTA: [c_lo, c_hi)
-      const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;
-      float m_run = -INFINITY, l_run = 0.f;      // of head fg (lanes 0..15), over this warp's tokens
-      float o[16][2];                            // O[head fg][latent 8 nb + 2 ft, + 1]
+    for (int c = 0; c < n_stages; ++c) {
+      const int slot = c % NQ;
+      // the slot was read by product (2) of tile c-2, whose completion is s_ready of that tile
+      if (c >= NQ && !mbar_wait(smem_u32(&sm.s_ready[slot]), (uint32_t)(((c / NQ) - 1) & 1), abort_flag)) break;
+      const int u = u_begin + c;
+      while (u >= sm.prefix[row + 1]) ++row;
+      const bool row_start = (c == 0) || (u == sm.prefix[row]);
+      if (row_start) {
+        const int b = p.batch_index ? p.batch_index[row] : row;
+        const int s0 = (u - sm.prefix[row]) * ST_TOK;
+        float sa, ca, sb, cb;
+        sincosf((float)s0 * f0, &sa, &ca);
+        sincosf((float)s0 * f1, &sb, &cb);
 #pragma unroll
-      for (int nb = 0; nb < 16; ++nb) { o[nb][0] = 0.f; o[nb][1] = 0.f; }
-
-      for (int c = c_lo; c < c_hi; ++c) {
-        if (dead || *abort_flag) { dead = true; continue; }
-        const int slot = c % NRING;
-        const uint32_t par = (uint32_t)((c / NRING) & 1);
-        const int vb = c % NBUF_V;
-        const int trole = warp == 0 ? 0 : (warp == 5 ? 1 : -1);
-        if (trole >= 0) TRACE(trole, c, 0);
-        if (!mbar_wait(smem_u32(&sm.q_full[slot]), par, abort_flag)) { dead = true; continue; }
-        if (!mbar_wait(smem_u32(&sm.t_ready[slot]), par, abort_flag)) { dead = true; continue; }
-        tc_fence_after();
-        if (trole >= 0) TRACE(trole, c, 1);
-        // ---------------- K rows from tensor memory: [RMSNorm,] RoPE, scores by mma.sync ----------------
-        const uint32_t k_addr = lane_addr + slot * 128;
-        const uint32_t* const qf = qf_lane + slot * (4 * 32 * 4);
-        if (warp == 0 && (lane & 3) == 0 && lane < 16) QDBG(1, c, lane >> 2, qf[0]);
-        float ss[2] = {0.f, 0.f};
-        float sa[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, sb[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-        {
-          float lo[8], hi[8];
-          tmem_ld_frag2(lo, hi, k_addr, k_addr + 64);
-          rope_scores<T, KNORM, 0>(lo, hi, ct, st, qf, sm.knorm_w, ft, ss, sa, sb);
-          tmem_ld_frag2(lo, hi, k_addr + 16, k_addr + 80);
-          rope_scores<T, KNORM, 1>(lo, hi, ct, st, qf, sm.knorm_w, ft, ss, sa, sb);
-          tmem_ld_frag2(lo, hi, k_addr + 32, k_addr + 96);
-          rope_scores<T, KNORM, 2>(lo, hi, ct, st, qf, sm.knorm_w, ft, ss, sa, sb);
-          tmem_ld_frag2(lo, hi, k_addr + 48, k_addr + 112);
-          // accumulator and query slot are released once the last read of each has been issued
-          tc_fence_before();
-          rope_scores<T, KNORM, 3>(lo, hi, ct, st, qf, sm.knorm_w, ft, ss, sa, sb);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm.acc_free[slot]));
-        if (trole >= 0) TRACE(trole, c, 2);
-
-        // ---------------- softmax weights of this warp's 16 tokens (private running maximum) ----------------
-        float s[2][2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) { s[e][0] = sa[e][0] + sb[e][0]; s[e][1] = sa[e][1] + sb[e][1]; }
-        if (KNORM) {
-          // 1/rms of the tokens: ss[e] holds a quarter of the squares of token (g + 8e); the scores of this thread
-          // belong to tokens 8e + 2t, 8e + 2t + 1, whose sums sit in the lanes with g = 2t, 2t + 1
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 1);
-            ss[e] += __shfl_xor_sync(0xffffffffu, ss[e], 2);
-            const float rs = rsqrtf(ss[e] * (1.0f / D) + p.k_norm_eps);
-            s[e][0] *= __shfl_sync(0xffffffffu, rs, 8 * ft);
-            s[e][1] *= __shfl_sync(0xffffffffu, rs, 8 * ft + 4);
+        for (int h = 0; h < HP; ++h) {
+          float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
+          if (h < G) {
+            const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)(g * G + h) * p.q_stride_h;
+            x0 = to_f32(qp[2 * lane]) * qscale; x1 = to_f32(qp[2 * lane + 64]) * qscale;
+            y0 = to_f32(qp[2 * lane + 1]) * qscale; y1 = to_f32(qp[2 * lane + 65]) * qscale;
           }
+          a0[h] = x0 * ca + x1 * sa; b0[h] = x1 * ca - x0 * sa;
+          a1[h] = y0 * cb + y1 * sb; b1[h] = y1 * cb - y0 * sb;
         }
-        const uint32_t vbits = sm.kvalid[c % KV_RING][cq] >> (16 * chf);
-        float mx = -INFINITY;
-#pragma unroll
-        for (int e = 0; e < 2; ++e)
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            const bool valid = head_lane && ((vbits >> (8 * e + 2 * ft + x)) & 1u);
-            if (!valid) s[e][x] = -INFINITY;
-            mx = fmaxf(mx, s[e][x]);
-          }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const bool grow = mx > m_run + M_SLACK;        // also the first tile with a token: -inf + slack = -inf
-        if (__any_sync(0xffffffffu, grow)) {
-          const float factor = grow ? ex2(m_run - mx) : 1.f;   // 0 when there was no maximum yet
-          if (grow) m_run = mx;
-          l_run *= factor;
-#pragma unroll
-          for (int nb = 0; nb < 16; ++nb) { o[nb][0] *= factor; o[nb][1] *= factor; }
-        }
-        const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-        float pr[2][2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e)
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            pr[e][x] = ex2(s[e][x] - m_use);
-            l_run += pr[e][x];
-          }
-        const uint32_t pa0 = Pack<T>::two(pr[0][0], pr[0][1]);   // tokens 2t, 2t+1      (k = 2t, 2t+1)
-        const uint32_t pa2 = Pack<T>::two(pr[1][0], pr[1][1]);   // tokens 8+2t, 8+2t+1  (k = 2t+8, 2t+9)
-
-        // ---------------- O += P^T . XV over the group's filled latent columns ----------------
-        if (trole >= 0) TRACE(trole, c, 3);
-        if (!mbar_wait(smem_u32(&sm.v_full[vb]), (uint32_t)((c / NBUF_V) & 1), abort_flag)) { dead = true; continue; }
-        if (trole >= 0) TRACE(trole, c, 4);
-        const int npair = sm.vfill[vb][vgrp];
-        const uint32_t v_addr = v_lane + vb * V_TILE_BYTES;
-#pragma unroll
-        for (int np = 0; np < 8; ++np) {
-          if (np < npair) {
-            uint32_t bm[4];
-            ldmatrix_x4_trans(bm, v_addr + np * 32);
-            mma_rows8<T>(o[2 * np][0], o[2 * np][1], pa0, pa2, bm[0], bm[1]);
-            mma_rows8<T>(o[2 * np + 1][0], o[2 * np + 1][1], pa0, pa2, bm[2], bm[3]);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm.v_free[vb]));
-        if (trole >= 0) TRACE(trole, c, 5);
-      }
-
-      // ---------------- row end: the eight warps merge their partials ----------------
-      // Warps 4..7 hand theirs to warps 0..3 (same fragment layout, so thread to thread), which merge and publish;
-      // then all 256 threads merge the four pair results, two (head, latent index) values each.
-      l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-      l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-      if (dead) m_run = -INFINITY;
-      const int pw = warp & 3;
-      if (head_lane && ft == 0) PDBG(warp, fg, m_run, l_run);
-      if (warp >= 4 && head_lane) {
-#pragma unroll
-        for (int nb = 0; nb < 16; ++nb)
-          *reinterpret_cast<float2*>(&sm.part_o[pw][fg][8 * nb + 2 * ft]) = make_float2(o[nb][0], o[nb][1]);
-        if (ft == 0) { sm.part_m[pw][fg] = m_run; sm.part_l[pw][fg] = l_run; }
-      }
-      __threadfence_block();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.row_sync));
-      if (!mbar_wait(smem_u32(&sm.row_sync), row_phase, abort_flag)) dead = true;
-      row_phase ^= 1u;
-      if (warp < 4 && head_lane) {
-        const float pm = sm.part_m[pw][fg], pl = sm.part_l[pw][fg];
-        const float M = fmaxf(m_run, pm);
-        const float f1 = (m_run == -INFINITY) ? 0.f : ex2(m_run - M);
-        const float f2 = (pm == -INFINITY) ? 0.f : ex2(pm - M);
-#pragma unroll
-        for (int nb = 0; nb < 16; ++nb) {
-          float2* cell = reinterpret_cast<float2*>(&sm.part_o[pw][fg][8 * nb + 2 * ft]);
-          const float2 po = *cell;
-          *cell = make_float2(fmaf(o[nb][0], f1, po.x * f2), fmaf(o[nb][1], f1, po.y * f2));
-        }
-        if (ft == 0) { sm.part_m[pw][fg] = M; sm.part_l[pw][fg] = fmaf(l_run, f1, pl * f2); }
-      }
-      __threadfence_block();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.row_sync));
-      if (!mbar_wait(smem_u32(&sm.row_sync), row_phase, abort_flag)) dead = true;
-      row_phase ^= 1u;
-      {
-        float* rec = nullptr;
-        if (!FUSED) {
-          // partial record (row, cta) -> entry row + blockIdx.x of this KV head
-          float* ws = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.workspace) + ws_header_bytes());
-          const size_t entries_per_group = (size_t)p.batch + n_cta;
-          rec = ws + (((size_t)g * entries_per_group + (size_t)row + blockIdx.x) * HP) * PART_STRIDE;
-        }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int e = tid + 256 * k, h = e >> 7, r = e & 127;
-          float M = -INFINITY;
-#pragma unroll
-          for (int w = 0; w < N_CW / 2; ++w) M = fmaxf(M, sm.part_m[w][h]);
-          float acc = 0.f, L = 0.f;
-#pragma unroll
-          for (int w = 0; w < N_CW / 2; ++w) {
-            const float mw = sm.part_m[w][h];
-            const float wt = (mw == -INFINITY) ? 0.f : ex2(mw - M);
-            acc = fmaf(sm.part_o[w][h][r], wt, acc);
-            L = fmaf(sm.part_l[w][h], wt, L);
-          }
-          if (!FUSED) {
-            rec[h * PART_STRIDE + 2 + r] = acc;
-            if (r == 0) { rec[h * PART_STRIDE] = M; rec[h * PART_STRIDE + 1] = L; }
-          } else {
-            if (r == 0) PDBG(8, h, M, L);
-            sm.lat[h][r] = L > 0.f ? acc / L : 0.f;
-            if (L <= 0.f && r == 0 && h < G) set_status(p.status, DKV_ST_EMPTY_ROW);
-            // the up-projection is done by the whole block after the pipeline has drained (a fused CTA has one row)
-          }
-        }
-      }
-      __threadfence_block();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.row_sync));     // the partial buffers may be rewritten after this
-      if (!mbar_wait(smem_u32(&sm.row_sync), row_phase, abort_flag)) dead = true;
-      row_phase ^= 1u;
-      ++row;
-    }
-    }   // compute warps
-  } else {
-    set_max_regs_dec<REGS_OTHER>();
-    proxy_fence_async();     // the basis was written with ordinary stores and is read by the tensor core
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (n_stages <= 0) {
-      // nothing to do for this CTA (fewer tiles than CTAs, or an empty row): straight to the epilogue
-    } else {
-      // =========================== gather warps ===========================
-      // Lane l of gather warp j owns token 32j + l of every tile: it stages the token's length and offset (cp.async,
-      // PD tiles ahead, slots private to the lane) and copies the coefficient row, one 16-byte chunk per cp.async.
-      //   K: chunk c of token t at c*2048 + t*16 (the tensor core's K-major operand layout); chunks past the row's
-      //      length are zero-filled (source size 0), so the tensor core always sees a full 128 x 128 tile.
-      //      The first K warp also issues the K reconstruction of the tile before (one lane, tcgen05.mma).
-      //   V: chunk c of token t at t*272 + c*16; zero-filled only up to the longest row of the token's 16-token
-      //      group, rounded to 16 latent columns -- the compute warp that owns the group reads no further.
-      //      V warp h also publishes the tile's rotated query of head h.
-      const bool is_v = warp >= W_VG0;
-      const int gw = (warp - W_KG0) & 3;
-      const dkv_side& sd = is_v ? p.v : p.k;
-      const int side = is_v ? 1 : 0;
-      const int t = 32 * gw + lane;
-      // the batch row a tile belongs to, tracked separately for the metadata prefetch (PD tiles ahead) and the copies
-      int pre_row = row0, pre_end = -1, pre_first = 0, pre_tokens = 0, pre_arena = 0;
-      int cur_row = row0, cur_end = -1, cur_arena = 0;
-      auto prefetch_meta = [&](int c) {   // no commit: the caller groups it with the tile's data copies
-        if (c < n_stages) {
-          const int u = u_begin + c;
-          if (u >= pre_end) {
-            while (u >= sm.prefix[pre_row + 1]) ++pre_row;
-            pre_arena = (p.batch_index ? p.batch_index[pre_row] : pre_row) * p.arenas_per_batch + g;
-            pre_tokens = row_tokens(p, pre_row);
-            pre_first = sm.prefix[pre_row];
-            pre_end = sm.prefix[pre_row + 1];
-          }
-          const int s0 = (u - pre_first) * ST_TOK;
-          int(*dst)[ST_TOK] = sm.meta[side][c % MSLOT];
-          if (s0 + t < pre_tokens) {
-            cp_async4(smem_u32(&dst[0][t]), sd.lens + (size_t)pre_arena * sd.lens_stride_a + s0 + t);
-            cp_async4(smem_u32(&dst[1][t]), sd.offs + (size_t)pre_arena * sd.offs_stride_a + s0 + t);
-          } else {
-            dst[0][t] = 0; dst[1][t] = 0;
-          }
-        }
-      };
-      // this tile's row of the token: validated length and source address
-      auto token_row = [&](int c, int& len) -> const unsigned char* {
-        const int u = u_begin + c;
-        if (u >= cur_end) {
-          while (u >= sm.prefix[cur_row + 1]) ++cur_row;
-          cur_arena = (p.batch_index ? p.batch_index[cur_row] : cur_row) * p.arenas_per_batch + g;
-          cur_end = sm.prefix[cur_row + 1];
-        }
-        int(*mt)[ST_TOK] = sm.meta[side][c % MSLOT];
-        len = mt[0][t];
-        const int off = mt[1][t];
-        if (((len | off) & 7) != 0 || len < 0 || len > R || off < 0 || (int64_t)off + len > sd.flat_stride) {
-          set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
-          len = 0;
-        }
-        return reinterpret_cast<const unsigned char*>(reinterpret_cast<const T*>(sd.flat) + (size_t)cur_arena * sd.flat_stride +
-                                                      (len > 0 ? off : 0));
-      };
-      for (int c = 0; c < PD; ++c) { prefetch_meta(c); cp_async_commit(); }   // groups 0..PD-1
-
-      if (!is_v) {
-        // ---------------------------------- K side ----------------------------------
-        const bool issuer = warp == W_KG0;
-        const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;   // 0 = f16, 1 = bf16
-        const uint32_t idesc_k = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-        // product (1) of tile j: K = X . Bk into accumulator j % NRING, once the operand tile has landed and the
-        // compute warps have read the accumulator's previous contents (tile j - NRING)
-        auto issue = [&](int j) -> bool {
-          const int slot = j % NRING;
-          const uint32_t par = (uint32_t)((j / NRING) & 1);
-          TRACE(2, j, 0);
-          if (j >= NRING && !mbar_wait(smem_u32(&sm.acc_free[slot]), par ^ 1u, abort_flag)) return false;
-          TRACE(2, j, 1);
-          if (!mbar_wait(smem_u32(&sm.a_full[slot]), par, abort_flag)) return false;
-          TRACE(2, j, 2);
-          if (lane == 0) {
-            proxy_fence_async();   // the tile was written by cp.async (generic proxy), the tensor core reads it through the async proxy
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(sm.a_tile[0]) + slot * TILE_BYTES;
-            const uint32_t basis_addr = smem_u32(sm.basis);
-            const uint32_t d_addr = tmem_base + slot * 128;
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              // A: K-major, 8-row core matrices 128 B apart (SBO), the two 8-coefficient chunks 2048 B apart (LBO)
-              // B: MN-major, 8-column core matrices 128 B apart (SBO), the two 8-row groups 2048 B apart (LBO)
-              umma_f16(d_addr, umma_desc(a_addr + ks * 4096, 2048, 128), umma_desc(basis_addr + ks * 4096, 2048, 128),
-                       idesc_k, ks > 0 ? 1u : 0u);
-            }
-            umma_commit(smem_u32(&sm.t_ready[slot]));   // also frees the operand tile (the K gather warps wait on it)
-          }
-          __syncwarp();
-          TRACE(2, j, 3);
-          return true;
-        };
-        bool ok = true;
-        for (int c = 0; c < n_stages && ok; ++c) {
-          const int buf = c % NRING;
-          if (issuer) TRACE(3, c, 0);
-          cp_async_wait<PD - 1>();   // group c (this tile's metadata) is complete
-          int len;
-          const unsigned char* row_src = token_row(c, len);
-          // product (1) of tile c - NRING must be done with this buffer: its completion is t_ready
-          if (c >= NRING && !mbar_wait(smem_u32(&sm.t_ready[buf]), (uint32_t)(((c / NRING) - 1) & 1), abort_flag)) break;
-          if (issuer) TRACE(3, c, 1);
-          const uint32_t m = __ballot_sync(0xffffffffu, len > 0);
-          if (lane == 0) sm.kvalid[c % KV_RING][gw] = m;
-          const uint32_t dst = smem_u32(sm.a_tile[buf]) + t * 16;
-#pragma unroll
-          for (int ch = 0; ch < 16; ++ch) {
-            // past the row's length the source size is 0: nothing is read from the (then meaningless) address
-            cp_async16_zfill(dst + ch * 2048, row_src + ch * 16, ch * 8 < len ? 16 : 0);
-          }
-          // The tile is handed over by the copy engine itself: each lane's arrival on the tile's barrier fires when
-          // its copies have landed.  One ordinary arrival per warp carries the warp's plain store (validity mask).
-          cp_async_arrive_when_landed(smem_u32(&sm.a_full[buf]));
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&sm.a_full[buf]));
-          prefetch_meta(c + PD);
-          cp_async_commit();                       // group PD + c
-          if (issuer) TRACE(3, c, 2);
-          if (issuer && c >= 1) ok = issue(c - 1);   // one tile behind the copies, so the wait for them is short
-        }
-        if (issuer && ok) issue(n_stages - 1);
       } else {
-        // ---------------------------------- V side ----------------------------------
-        // Rotated query of head hv: Q~ = scale * R(-s0) q for the tile's base position s0, written as mma.sync A
-        // fragments (row hv), so that q~ . R(t) k = q . R(s0 + t) k with the in-tile offset t = 0..127 (the rotation
-        // the compute warps apply).  Lane l owns the pairs j = 2l, 2l+1.
-        const int hv = gw;
-        const float f0 = expf(-((float)(4 * lane) / (float)D) * log_theta);
-        const float f1 = expf(-((float)(4 * lane + 2) / (float)D) * log_theta);
-        float cd0, sd0, cd1, sd1;     // rotation by one tile
-        sincosf((float)ST_TOK * f0, &sd0, &cd0);
-        sincosf((float)ST_TOK * f1, &sd1, &cd1);
-        const float qscale = rsqrtf((float)D) * 1.4426950408889634f;  // softmax scale and log2(e) folded into q
-        float a0 = 0.f, b0 = 0.f, a1 = 0.f, b1 = 0.f;   // (q~_j, q~_{j+64}) for j = 2l and j = 2l+1
-        // fragment cell of this lane's dims (2l, 2l+1): k-step pair i = l / 8, register a0a1 or a4a5, thread 4 hv + l % 4
-        uint32_t* const qf_w = &sm.qfrag[0][lane >> 3][4 * hv + (lane & 3)][(lane & 7) >> 2];
-        int qrow = row0;
-        for (int c = 0; c < n_stages; ++c) {
-          const int buf = c % NBUF_V, slot = c % NRING;
-          if (warp == W_VG0) TRACE(4, c, 0);
-          // ---- rotated query (slot last read by the compute warps in tile c - NRING) ----
-          if (c >= NRING && !mbar_wait(smem_u32(&sm.acc_free[slot]), (uint32_t)(((c / NRING) - 1) & 1), abort_flag)) break;
-          {
-            const int u = u_begin + c;
-            while (u >= sm.prefix[qrow + 1]) ++qrow;
-            if (c == 0 || u == sm.prefix[qrow]) {
-              const int b = p.batch_index ? p.batch_index[qrow] : qrow;
-              const int s0 = (u - sm.prefix[qrow]) * ST_TOK;
-              float sa, ca, sb, cb;
-              sincosf((float)s0 * f0, &sa, &ca);
-              sincosf((float)s0 * f1, &sb, &cb);
-              float x0 = 0.f, x1 = 0.f, y0 = 0.f, y1 = 0.f;
-              if (hv < G) {
-                const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)(g * G + hv) * p.q_stride_h;
-                x0 = to_f32(qp[2 * lane]) * qscale; x1 = to_f32(qp[2 * lane + 64]) * qscale;
-                y0 = to_f32(qp[2 * lane + 1]) * qscale; y1 = to_f32(qp[2 * lane + 65]) * qscale;
-              }
-              a0 = x0 * ca + x1 * sa; b0 = x1 * ca - x0 * sa;
-              a1 = y0 * cb + y1 * sb; b1 = y1 * cb - y0 * sb;
-            } else {
-              const float x0 = a0, x1 = b0, y0 = a1, y1 = b1;
-              a0 = x0 * cd0 + x1 * sd0; b0 = x1 * cd0 - x0 * sd0;
-              a1 = y0 * cd1 + y1 * sd1; b1 = y1 * cd1 - y0 * sd1;
-            }
-            uint32_t* const w0 = qf_w + slot * (4 * 32 * 4);
-            w0[0] = Pack<T>::two(a0, a1);          // dims 2l, 2l+1     -> k-step i
-            if (lane == 0) QDBG(0, c, hv, Pack<T>::two(a0, a1));
-            w0[2] = Pack<T>::two(b0, b1);          // dims 2l+64, 2l+65 -> k-step 4 + i
-            __threadfence_block();   // every lane's stores must be performed before lane 0 announces them
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm.q_full[slot]));
-          }
-          if (warp == W_VG0) TRACE(4, c, 1);
-          // ---- V rows ----
-          cp_async_wait<PD - 1>();   // group c (this tile's metadata) is complete
-          int len;
-          const unsigned char* row_src = token_row(c, len);
-          // the 8 compute warps must be done with the tile that was in this buffer NBUF_V tiles ago
-          if (c >= NBUF_V && !mbar_wait(smem_u32(&sm.v_free[buf]), (uint32_t)(((c / NBUF_V) - 1) & 1), abort_flag)) break;
-          if (warp == W_VG0) TRACE(4, c, 2);
-          int gmax = len;   // longest row of this lane's 16-token group
 #pragma unroll
-          for (int o = 1; o < 16; o <<= 1) gmax = max(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
-          const int npair = (gmax + 15) >> 4;                      // 16-column pairs this group needs
-          const int wpair = max(npair, __shfl_xor_sync(0xffffffffu, npair, 16));
-          if ((lane & 15) == 0) sm.vfill[buf][2 * gw + (lane >> 4)] = npair;
-          const uint32_t dst = smem_u32(sm.v_tile[buf]) + t * V_PITCH;
-#pragma unroll
-          for (int ch = 0; ch < 16; ++ch) {
-            if (ch < 2 * wpair) {            // warp-uniform
-              if (ch < 2 * npair) cp_async16_zfill(dst + ch * 16, row_src + ch * 16, ch * 8 < len ? 16 : 0);
-            }
-          }
-          cp_async_arrive_when_landed(smem_u32(&sm.v_full[buf]));
-          __threadfence_block();   // lanes 0 and 16 stored the fill widths
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&sm.v_full[buf]));   // carries the plain store of the fill width
-          prefetch_meta(c + PD);
-          cp_async_commit();                       // group PD + c
-          if (warp == W_VG0) TRACE(4, c, 3);
+        for (int h = 0; h < HP; ++h) {
+          const float x0 = a0[h], x1 = b0[h], y0 = a1[h], y1 = b1[h];
+          a0[h] = x0 * cd0 + x1 * sd0; b0[h] = x1 * cd0 - x0 * sd0;
+          a1[h] = y0 * cd1 + y1 * sd1; b1[h] = y1 * cd1 - y0 * sd1;
         }
       }
-      cp_async_wait<0>();
+      unsigned char* const w0 = sm.qrot[slot] + (lane >> 2) * Q_LBO + (lane & 3) * 4;
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        *reinterpret_cast<uint32_t*>(w0 + h * 16) = Pack<T>::two(a0[h], a1[h]);                 // dims 2l, 2l+1
+        *reinterpret_cast<uint32_t*>(w0 + h * 16 + 8 * Q_LBO) = Pack<T>::two(b0[h], b1[h]);     // dims 2l+64, 2l+65
+      }
+      proxy_fence_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.q_full[slot]));
     }
   }
+
+  else if (warp == W_KG0 || warp == W_KG0 + 4 || warp == W_VG0 || warp == W_VG0 + 4 || warp >= W_G2) {
+    // =========================== gather warps ===========================
+    // Four warps per side; lane l of gather warp j owns token 32j + l of every tile: it stages the token's length
+    // and offset (cp.async, PD tiles ahead, slots private to the lane) and copies the coefficient row into the
+    // operand tile, one 16-byte chunk per cp.async, chunk c of token t at c*2048 + t*16; chunks past the row's
+    // length are zero-filled (source size 0), so the tensor core always sees a full 128 x 128 tile.
+    const bool is_v = warp >= W_G2 ? warp >= W_G2 + 2 : (warp & 3) == (W_VG0 & 3);
+    const int gw = warp >= W_G2 ? 2 + ((warp - W_G2) & 1) : (warp >> 2) & 1;
+    const dkv_side& sd = is_v ? p.v : p.k;
+    const int side = is_v ? 1 : 0;
+    const int NB = is_v ? NBUF_V : NBUF_A;
+    const int t = 32 * gw + lane;
+    RowInfo pre{row0, 0, 0, 0}, cur{row0, 0, 0, 0};
+    int pre_end = -1, cur_end = -1;
+    auto prefetch_meta = [&](int c) {   // no commit: the caller groups it with the tile's data copies
+      if (c < n_stages) {
+        const int u = u_begin + c;
+        if (u >= pre_end) { enter_row(pre, u); pre_end = sm.prefix[pre.row + 1]; }
+        const int s0 = (u - pre.first_unit) * ST_TOK;
+        int(*dst)[ST_TOK] = sm.meta[side][c % MSLOT];
+        if (s0 + t < pre.tokens) {
+          cp_async4(smem_u32(&dst[0][t]), sd.lens + (size_t)pre.arena * sd.lens_stride_a + s0 + t);
+          cp_async4(smem_u32(&dst[1][t]), sd.offs + (size_t)pre.arena * sd.offs_stride_a + s0 + t);
+        } else {
+          dst[0][t] = 0; dst[1][t] = 0;
+        }
+      }
+    };
+    for (int c = 0; c < PD; ++c) { prefetch_meta(c); cp_async_commit(); }   // groups 0..PD-1
+    for (int c = 0; c < n_stages; ++c) {
+      const int buf = c % NB;
+      cp_async_wait<PD - 1>();   // group c (this tile's metadata) is complete
+      const int u = u_begin + c;
+      if (u >= cur_end) { enter_row(cur, u); cur_end = sm.prefix[cur.row + 1]; }
+      int(*mt)[ST_TOK] = sm.meta[side][c % MSLOT];
+      int len = mt[0][t];
+      const int off = mt[1][t];
+      if (((len | off) & 7) != 0 || len < 0 || len > R || off < 0 || (int64_t)off + len > sd.flat_stride) {
+        set_status(p.status, DKV_ST_BAD_LENGTH);   // breaks the layout contract: token dropped, call flagged
+        len = 0;
+      }
+      const unsigned char* row_src = reinterpret_cast<const unsigned char*>(
+          reinterpret_cast<const T*>(sd.flat) + (size_t)cur.arena * sd.flat_stride + (len > 0 ? off : 0));
+      // the tensor core must be done with the tile that was in this buffer NB tiles ago
+      // (K: product (1) of tile c-2 read this buffer; its completion is t_ready of that tile, ring of NBUF_T)
+      if (c >= NB) {
+        const uint32_t bar = is_v ? smem_u32(&sm.v_free[buf]) : smem_u32(&sm.t_ready[(c - NBUF_A) % NBUF_T]);
+        const uint32_t par = is_v ? (uint32_t)(((c / NBUF_V) - 1) & 1) : (uint32_t)(((c - NBUF_A) / NBUF_T) & 1);
+        if (!mbar_wait(bar, par, abort_flag)) break;
+      }
+      if (!is_v) {
+        // written after the wait: product (1) of tile c-3 is complete, so product (2) of tile c-6 has been issued,
+        // which needed the P tile of tile c-8 written -- the softmax warps are past the mask of tile c-8 (same slot)
+        const uint32_t m = __ballot_sync(0xffffffffu, len > 0);
+        if (lane == 0) sm.kvalid[c % KV_RING][gw] = m;
+      }
+      const uint32_t dst = smem_u32(is_v ? sm.v_tile[buf] : sm.a_tile[buf]) + t * 16;
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        // past the row's length the source size is 0: nothing is read from the (then meaningless) address
+        cp_async16_zfill(dst + ch * 2048, row_src + ch * 16, ch * 8 < len ? 16 : 0);
+      }
+      // The tile is handed over by the copy engine itself: each lane's arrival on the tile's barrier fires when
+      // its copies have landed, so the warp neither waits for the data nor delays the hand-over until it comes
+      // round again (which would put the next tile's wait for a free buffer into the serial loop
+      // buffer free -> copies -> product (1) -> buffer free).  The consumer issues the proxy fence.
+      cp_async_arrive_when_landed(smem_u32(is_v ? &sm.v_full[buf] : &sm.a_full[buf]));
+      prefetch_meta(c + PD);
+      cp_async_commit();                       // group PD + c
+    }
+    cp_async_wait<0>();
+  }
+
+  else if (warp == W_MMA) {
+    // =========================== tensor-core issuer A: products (1) and (2) ===========================
+    // One lane issues both products.  It never blocks on one barrier: it probes whether the next product (1) or
+    // (2) has its operands in place and issues what is ready, so that one group's RoPE pass does not hold back
+    // the other group's products.  The tensor core executes one thread's instructions in issue order, which also
+    // orders the re-use of the accumulator buffers: product (1) of tile i+3 is only issued after product (2) of
+    // tile i, which reads K' from the same buffer.  This thread is the serial part of the pipeline, so its code
+    // is kept short: fully unrolled issue loops over constant descriptors, probes issued back to back.
+    if (lane == 0) {
+      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;   // 0 = f16, 1 = bf16
+      const uint32_t idesc_k = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t basis_addr = smem_u32(sm.basis);
+      int ri = 0, qi = 0;     // next tile of products (1), (2)
+      int rt = 0, qt = 0;     // their accumulator buffers ri % 3, qi % 3 ...
+      uint32_t rtp = 0, qtp = 0;   // ... and phases (ri / 3) & 1, (qi / 3) & 1
+      uint32_t idle = 0;
+      while (qi < n_stages) {
+        static_assert(NBUF_A == NBUF_T, "the K operand tiles and the K accumulators share ring index and phase");
+        const int rb = rt, qg = qi & 1;
+        const bool r_ok = mbar_probe(smem_u32(&sm.a_full[rb]), rtp);
+        const bool k_ok = mbar_probe(smem_u32(&sm.kp_ready[qt]), qtp);
+        const bool q_ok = mbar_probe(smem_u32(&sm.q_full[qg]), (uint32_t)((qi >> 1) & 1)) &&
+                          (qi < 2 || mbar_probe(smem_u32(&sm.p_ready[qg]), (uint32_t)(((qi >> 1) - 1) & 1)));   // score tile read out
+        bool progress = false;
+        if (ri < n_stages && ri - qi < NBUF_T && r_ok) {
+          proxy_fence_async();   // the tile was written by cp.async (generic proxy), the tensor core reads it through the async proxy
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sm.a_tile[rb]);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            // A: K-major, 8-row core matrices 128 B apart (SBO), the two 8-coefficient chunks 2048 B apart (LBO)
+            // B: MN-major, 8-column core matrices 128 B apart (SBO), the two 8-row groups 2048 B apart (LBO)
+            umma_f16(tmem_base + TM_K + rt * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
+                     umma_desc(basis_addr + ks * 4096, 2048, 128), idesc_k, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&sm.t_ready[rt]));   // also frees the operand tile (the K gather warps wait on it too)
+          ++ri;
+          if (++rt == NBUF_T) { rt = 0; rtp ^= 1u; }
+          progress = true;
+        }
+        if (qi < ri && k_ok && q_ok && !(progress && qi + 1 == ri)) {
+          tc_fence_after();
+          const uint32_t q_addr = smem_u32(sm.qrot[qg]);
+          const uint32_t kp = tmem_base + TM_K + qt * 128;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            // A: K' of the tile, dims 16ks..16ks+15 = packed columns 8ks.. (dims < 64) or 64 + 8(ks-4).. (dims >= 64)
+            // B: K-major, head rows 16 B apart inside a core matrix, 8-row groups 128 B (SBO), dim chunks Q_LBO apart
+            umma_f16_ta(tmem_base + TM_S + 16 * qg, kp + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4)),
+                        umma_desc(q_addr + ks * 2 * Q_LBO, Q_LBO, 128), idesc_s, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&sm.s_ready[qg]));   // also frees the rotated queries (the rotator waits on it too)
+          ++qi;
+          if (++qt == NBUF_T) { qt = 0; qtp ^= 1u; }
+          progress = true;
+        }
+        if (progress) {
+          idle = 0;
+        } else {
+          ++idle;
+          if ((idle & 1023u) == 0u && *abort_flag) break;
+          if (idle >= SPIN_LIMIT) { *abort_flag = 1; break; }
+        }
+      }
+    }
+  }
+
+  else if (warp == W_MMA2) {
+    // =========================== tensor-core issuer B: product (3) ===========================
+    // A thread of its own (on another SM sub-partition), so that product (3) costs issuer A no time.
+    if (lane == 0) {
+      const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+      const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+      int row_pv = row0;
+      int c_row_lo = 0, c_row_hi = 0;   // tiles of the current batch row in this CTA: [c_row_lo, c_row_hi)
+      for (int c = 0; c < n_stages; ++c) {
+        const int grp = c & 1, vb = c % NBUF_V;
+        if (c >= c_row_hi) {
+          const int u = u_begin + c;
+          while (u >= sm.prefix[row_pv + 1]) ++row_pv;
+          c_row_lo = max(sm.prefix[row_pv], u_begin) - u_begin;
+          c_row_hi = sm.prefix[row_pv + 1] - u_begin;
+        }
+        const bool first = c == c_row_lo;   // the first tile of a row starts a new sum
+        if (!mbar_wait_thread(smem_u32(&sm.v_full[vb]), (uint32_t)((c / NBUF_V) & 1), abort_flag)) break;
+        if (!mbar_wait_thread(smem_u32(&sm.p_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
+        proxy_fence_async();   // V tile written by cp.async
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sm.v_tile[vb]), p_addr = smem_u32(sm.p_tile[grp]);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // A = XV^T: MN-major, 16 tokens per step (256 B), token groups of 8 are 128 B apart (LBO), latent
+          //     chunks 2048 B apart (SBO)
+          // B = P:    MN-major, token groups of 8 are 128 B apart (LBO); the second group of 8 columns aliases
+          //     the first (SBO 0): columns 8..15 of the result duplicate 0..7 and are never read
+          umma_f16(tmem_base + TM_O, umma_desc(v_addr + ks * 256, 128, 2048),
+                   umma_desc(p_addr + ks * 256, 128, 0), idesc_o, (ks > 0 || !first) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sm.pv_done[grp]));
+        umma_commit(smem_u32(&sm.v_free[vb]));
+      }
+    }
+  }
+
+  else if (warp < 4) {
+    // ============================= RoPE warps =============================
+    // Thread (warp, lane) owns token 32 warp + lane of every tile, which is tensor-memory lane 32 warp + lane --
+    // the lanes a warp in SM sub-partition `warp` may access.  It turns the K row of product (1) into K' for
+    // product (2); it knows nothing about batch rows.
+    const int tok = tid;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * warp) << 16);
+    int buf = 0;            // accumulator buffer c % 3 and its phase (c / 3) & 1
+    uint32_t bpar = 0;
+    for (int c = 0; c < n_stages; ++c) {
+      if (!mbar_wait(smem_u32(&sm.t_ready[buf]), bpar, abort_flag)) break;
+      tc_fence_after();
+      const uint32_t k_addr = lane_addr + TM_K + 128 * buf;
+      // ---------------- K row from tensor memory: [RMSNorm,] RoPE, K' back as packed 16-bit pairs ----------------
+      float ss = 0.f;
+#pragma unroll 1   // kept rolled: the warp roles of an SM sub-partition share a small instruction cache
+      for (int i = 0; i < 8; ++i) {
+        // pairs j = 8i..8i+7: dims j (columns 8i..) and j+64 (columns 64+8i..); table cells 8i..: per two pairs
+        // one word {cos_j, cos_j+1} and one word {sin_j, sin_j+1} in fp16
+        float lo[8], hi[8];
+        uint32_t tg[8];
+        tmem_ld_rope_chunk(lo, hi, tg, k_addr + 8 * i, k_addr + 64 + 8 * i, lane_addr + TM_TRIG + 8 * i);
+        if (KNORM) {
+          // RMSNorm of K (Qwen3): the weight is applied here, the per-token 1/rms scales the score later
+          const float4 w0 = *reinterpret_cast<const float4*>(&sm.knorm_w[8 * i]);
+          const float4 w1 = *reinterpret_cast<const float4*>(&sm.knorm_w[8 * i + 4]);
+          const float4 w2 = *reinterpret_cast<const float4*>(&sm.knorm_w[64 + 8 * i]);
+          const float4 w3 = *reinterpret_cast<const float4*>(&sm.knorm_w[64 + 8 * i + 4]);
+          const float wl[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          const float wh[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            ss = fmaf(lo[e], lo[e], fmaf(hi[e], hi[e], ss));
+            lo[e] *= wl[e];
+            hi[e] *= wh[e];
+          }
+        }
+        uint32_t plo[4], phi[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const float2 L = make_float2(lo[2 * m], lo[2 * m + 1]), H = make_float2(hi[2 * m], hi[2 * m + 1]);
+          const float2 C = __half22float2(*reinterpret_cast<const __half2*>(&tg[2 * m]));
+          const float2 S = __half22float2(*reinterpret_cast<const __half2*>(&tg[2 * m + 1]));
+          const float2 u = __fmul2_rn(H, S);
+          const float2 lo2 = __ffma2_rn(L, C, make_float2(-u.x, -u.y));
+          const float2 hi2 = __ffma2_rn(L, S, __fmul2_rn(H, C));
+          plo[m] = Pack<T>::two(lo2.x, lo2.y);
+          phi[m] = Pack<T>::two(hi2.x, hi2.y);
+        }
+        // packed columns 4i.. (dims 8i..8i+7) and 64+4i.. (dims 64+8i..): both lie inside columns already read
+        tmem_st4(k_addr + 4 * i, plo[0], plo[1], plo[2], plo[3]);
+        tmem_st4(k_addr + 64 + 4 * i, phi[0], phi[1], phi[2], phi[3]);
+      }
+      if (KNORM) sm.rs_buf[c % RS_RING][tok] = rsqrtf(ss * (1.0f / D) + p.k_norm_eps);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.kp_ready[buf]));
+      if (++buf == NBUF_T) { buf = 0; bpar ^= 1u; }
+    }
+  }
+
+  else if (warp < NCW) {
+  // ============================= softmax warps =============================
+  // Thread (wq, lane) owns token 32 wq + lane of every tile: it reads the token's scores from product (2),
+  // forms the softmax weights against the reference maximum m_ref shared by the four warps, and stores P for
+  // product (3).  These warps follow the batch rows and write each row's result.
+  const int wq = warp & 3;
+  const int tok = 32 * wq + lane;
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * wq) << 16);
+  const uint32_t o_addr = lane_addr + TM_O;
+
+  int row = row0;
+  while (row < p.batch && sm.prefix[row] < u_end) {
+    const int c_lo = max(sm.prefix[row], u_begin) - u_begin;     // tiles of this row in this CTA: [c_lo, c_hi)
+    const int c_hi = min(sm.prefix[row + 1], u_end) - u_begin;
+    float m_ref[HP], l_part[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) { m_ref[h] = -INFINITY; l_part[h] = 0.f; }
+    int c_last = -1;            // last tile of the row that was processed
+    bool dead = false;
+
+    for (int c = c_lo; c < c_hi; ++c) {
+      if (dead || *abort_flag) { dead = true; continue; }
+      const int buf = c & 1;
+      const uint32_t par = (uint32_t)((c >> 1) & 1);
+      const bool first = c == c_lo;     // O holds nothing of this row yet
+      // ---------------- scores of this token for the group's heads ----------------
+      if (!mbar_wait(smem_u32(&sm.s_ready[buf]), par, abort_flag)) { dead = true; continue; }
+      tc_fence_after();
+      float s[HP];
+      tmem_ld4(s, lane_addr + TM_S + 16 * buf);
+      if (KNORM) {
+        const float rs = sm.rs_buf[c % RS_RING][tok];
+#pragma unroll
+        for (int h = 0; h < HP; ++h) s[h] *= rs;
+      }
+      const bool valid = (sm.kvalid[c % KV_RING][wq] >> lane) & 1u;
+      float mx[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        if (!valid) s[h] = -INFINITY;
+        mx[h] = warp_max_redux(s[h]);
+      }
+      // tile maxima: the four warps meet on an mbarrier (bounded wait, unlike a named barrier)
+      if (lane == 0) {
+        *reinterpret_cast<float4*>(sm.tmax[buf][wq]) = make_float4(mx[0], mx[1], mx[2], mx[3]);
+        mbar_arrive(smem_u32(&sm.grp_sync));
+      }
+      if (!mbar_wait(smem_u32(&sm.grp_sync), (uint32_t)(c & 1), abort_flag)) { dead = true; continue; }
+      float factor[HP];
+      bool grow = false;
+      {
+        const float4 t0 = *reinterpret_cast<const float4*>(sm.tmax[buf][0]);
+        const float4 t1 = *reinterpret_cast<const float4*>(sm.tmax[buf][1]);
+        const float4 t2 = *reinterpret_cast<const float4*>(sm.tmax[buf][2]);
+        const float4 t3 = *reinterpret_cast<const float4*>(sm.tmax[buf][3]);
+        const float tm[HP] = {fmaxf(fmaxf(t0.x, t1.x), fmaxf(t2.x, t3.x)), fmaxf(fmaxf(t0.y, t1.y), fmaxf(t2.y, t3.y)),
+                              fmaxf(fmaxf(t0.z, t1.z), fmaxf(t2.z, t3.z)), fmaxf(fmaxf(t0.w, t1.w), fmaxf(t2.w, t3.w))};
+#pragma unroll
+        for (int h = 0; h < HP; ++h) {
+          factor[h] = 1.f;
+          if (tm[h] > m_ref[h] + M_SLACK) {   // also the first tile with a token: -inf + slack = -inf
+            factor[h] = exp2f(m_ref[h] - tm[h]);   // 0 when there was no reference yet
+            m_ref[h] = tm[h];
+            grow = true;
+          }
+        }
+      }
+      // the P tile of this parity was read by product (3) of tile c-2
+      if (c >= 2 && !mbar_wait(smem_u32(&sm.pv_done[buf]), (uint32_t)(((c >> 1) - 1) & 1), abort_flag)) { dead = true; continue; }
+      if (grow) {   // uniform over the four warps: every thread sees the same maxima
+#pragma unroll
+        for (int h = 0; h < HP; ++h) l_part[h] *= factor[h];
+        if (!first) {
+          // O is rescaled in tensor memory: product (3) of tile c-1 must be complete as well
+          if (!mbar_wait(smem_u32(&sm.pv_done[buf ^ 1]), (uint32_t)(((c - 1) >> 1) & 1), abort_flag)) { dead = true; continue; }
+          tc_fence_after();
+          float o[4];
+          tmem_ld4(o, o_addr);
+          tmem_st4(o_addr, __float_as_uint(o[0] * factor[0]), __float_as_uint(o[1] * factor[1]),
+                   __float_as_uint(o[2] * factor[2]), __float_as_uint(o[3] * factor[3]));
+          tmem_wait_st();
+        }
+      }
+      float pr[HP];
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        pr[h] = exp2f(s[h] - (m_ref[h] == -INFINITY ? 0.f : m_ref[h]));
+        l_part[h] += pr[h];
+      }
+      *reinterpret_cast<uint4*>(sm.p_tile[buf] + tok * 16) = make_uint4(Pack<T>::two(pr[0], pr[1]), Pack<T>::two(pr[2], pr[3]), 0u, 0u);
+      proxy_fence_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[buf]));
+      c_last = c;
+    }
+
+    // ---------------- row flush ----------------
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    if (c_last >= 0 && !dead && mbar_wait(smem_u32(&sm.pv_done[c_last & 1]), (uint32_t)((c_last >> 1) & 1), abort_flag)) {
+      tc_fence_after();
+      tmem_ld4(o, o_addr);   // O^T[r = tok][head]
+    }
+#pragma unroll
+    for (int h = 0; h < HP; ++h) {
+      const float l = warp_sum(l_part[h]);
+      if (lane == 0) sm.lsum[wq][h] = l;
+    }
+    consumer_bar();
+    float L[HP];
+#pragma unroll
+    for (int h = 0; h < HP; ++h) L[h] = (sm.lsum[0][h] + sm.lsum[1][h]) + (sm.lsum[2][h] + sm.lsum[3][h]);
+    if (!FUSED) {
+      // partial record (row, cta) -> entry row + blockIdx.x of this KV head
+      float* ws = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(p.workspace) + ws_header_bytes());
+      const size_t entries_per_group = (size_t)p.batch + n_cta;
+      float* rec = ws + (((size_t)g * entries_per_group + (size_t)row + blockIdx.x) * HP) * PART_STRIDE;
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        rec[h * PART_STRIDE + 2 + tok] = o[h];
+        if (tok == 0) { rec[h * PART_STRIDE] = m_ref[h]; rec[h * PART_STRIDE + 1] = L[h]; }
+      }
+      consumer_bar();   // lsum may be rewritten by the next row
+    } else {
+#pragma unroll
+      for (int h = 0; h < HP; ++h) {
+        sm.lat[h][tok] = L[h] > 0.f ? o[h] / L[h] : 0.f;
+        if (L[h] <= 0.f && tok == 0 && h < G) set_status(p.status, DKV_ST_EMPTY_ROW);
+      }
+      // the up-projection is done by the whole block after the pipeline has drained (a fused CTA has one row)
+    }
+    ++row;
+  }
+  }   // softmax warps
 
   // ---- epilogue: every warp arrives here; the tensor memory is returned by the warp that allocated it ----
   tc_fence_before();
@@ -894,7 +910,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       op[d] = from_f32<T>(acc0 + acc1);
     }
   }
-  if (warp == W_KG0) {
+  if (warp == W_MMA) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
   }
@@ -1123,18 +1139,3 @@ int mma_two_stage_noalloc(const dkv_attn_args* a) {
 }
 
 }  // namespace dkv
-
-#ifdef DKV_TRACE
-extern "C" int dkv_debug_p(float* host, size_t bytes) {
-  if (bytes > sizeof(dkv::g_pdbg)) bytes = sizeof(dkv::g_pdbg);
-  return (int)cudaMemcpyFromSymbol(host, dkv::g_pdbg, bytes);
-}
-extern "C" int dkv_debug_q(unsigned int* host, size_t bytes) {
-  if (bytes > sizeof(dkv::g_qdbg)) bytes = sizeof(dkv::g_qdbg);
-  return (int)cudaMemcpyFromSymbol(host, dkv::g_qdbg, bytes);
-}
-extern "C" int dkv_debug_trace(long long* host, size_t bytes) {
-  if (bytes > sizeof(dkv::g_trace)) bytes = sizeof(dkv::g_trace);
-  return (int)cudaMemcpyFromSymbol(host, dkv::g_trace, bytes);
-}
-#endif

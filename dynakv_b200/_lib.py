@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libdynakv_b200.so")
 
 DKV_F32, DKV_F16, DKV_BF16 = 0, 1, 2
-ST_OVERFLOW, ST_BAD_LENGTH, ST_EMPTY_ROW = 1, 2, 4
+ST_OVERFLOW, ST_BAD_LENGTH, ST_EMPTY_ROW, ST_TIMEOUT = 1, 2, 4, 8
 
 _DTYPES = {torch.float32: DKV_F32, torch.float16: DKV_F16, torch.bfloat16: DKV_BF16}
 
@@ -48,6 +48,7 @@ class AttnArgs(C.Structure):
         ("out", C.c_void_p), ("out_stride_b", C.c_int64), ("out_stride_h", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p), ("n_sm", C.c_int32), ("stream", C.c_void_p),
+        ("route_min_tokens", C.c_int32), ("route_max_tokens", C.c_int32),
     ]
 
 

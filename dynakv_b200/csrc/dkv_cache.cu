@@ -12,19 +12,21 @@ __device__ __forceinline__ void copy_row(T* dst, const T* src, int n, int lane) 
   for (int i = lane; i < n; i += 32) dst[i] = src[i];
 }
 
-// Validate a length against [0, max_dim] and the declared step; returns the sanitised value.
+// Validate a length against [0, max_dim] and the declared step; returns the sanitised value.  A length that is not
+// a multiple of the step is rounded UP (capped at max_dim): the stored row is then a superset of what the caller
+// asked to keep, never a truncation of it.  Either way the call is flagged.
 __device__ __forceinline__ int checked_len(int len, int max_dim, int step, int32_t* status, int lane) {
   bool bad = (len < 0) || (len > max_dim) || (step > 1 && (len % step) != 0);
   if (bad) {
     if (lane == 0) set_status(status, DKV_ST_BAD_LENGTH);
     len = min(max(len, 0), max_dim);
-    if (step > 1) len -= len % step;
+    if (step > 1 && (len % step) != 0) len = min(len + step - len % step, max_dim - max_dim % step);
   }
   return len;
 }
 
 // One block per batch row; each warp owns one (arena, side) row at a time.
-template <typename T, bool PROJECT>
+template <typename T>
 __global__ void __launch_bounds__(512) append_decode_kernel(dkv_append_args p) {
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
@@ -42,23 +44,15 @@ __global__ void __launch_bounds__(512) append_decode_kernel(dkv_append_args p) {
     len = checked_len(len, p.max_dim, p.len_multiple, p.status, lane);
     const int off = sd.ptr[a];
     if ((int64_t)off + len > sd.flat_stride) {
-      if (lane == 0) set_status(p.status, DKV_ST_OVERFLOW);
+      if (lane == 0) {   // the token is recorded as empty, so that attention never reads stale metadata for it
+        set_status(p.status, DKV_ST_OVERFLOW);
+        sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = 0;
+        sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
+      }
       continue;
     }
     T* dst = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride + off;
-    if (PROJECT) {
-      // coefficient r = sum_d x[d] * basis[j, r, d]  (fp32 accumulate, d ascending)
-      const T* basis = reinterpret_cast<const T*>(side_idx ? p.v_basis : p.k_basis) +
-                       (size_t)j * p.max_dim * p.max_dim;
-      for (int r = lane; r < len; r += 32) {
-        const T* row = basis + (size_t)r * p.max_dim;
-        float acc = 0.f;
-        for (int d = 0; d < p.max_dim; ++d) acc = fmaf(to_f32(src[d]), to_f32(row[d]), acc);
-        dst[r] = from_f32<T>(acc);
-      }
-    } else {
-      copy_row(dst, src, len, lane);
-    }
+    copy_row(dst, src, len, lane);
     __syncwarp();
     if (lane == 0) {
       sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = len;
@@ -96,7 +90,11 @@ __global__ void __launch_bounds__(1024) append_project_kernel(dkv_append_args p,
     len = checked_len(len, 128, p.len_multiple, p.status, lane + sub);
     const int off = sd.ptr[a];
     if ((int64_t)off + len > sd.flat_stride) {
-      if (lane == 0 && sub == 0) set_status(p.status, DKV_ST_OVERFLOW);
+      if (lane == 0 && sub == 0) {   // recorded as an empty token (the pointer pass below then adds nothing)
+        set_status(p.status, DKV_ST_OVERFLOW);
+        sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = 0;
+        sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
+      }
       continue;
     }
     T* dst = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride + off;
@@ -209,8 +207,9 @@ __global__ void __launch_bounds__(256) decompress_kernel(dkv_side sd, T* dense, 
   const int a = blockIdx.y, lane = threadIdx.x & 31;
   const int s = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (s >= n_tok) return;
-  const int len = min(sd.lens[(size_t)a * sd.lens_stride_a + (size_t)s * sd.lens_stride_s], max_dim);
-  const int off = sd.offs[(size_t)a * sd.offs_stride_a + (size_t)s * sd.offs_stride_s];
+  int len = min(max(sd.lens[(size_t)a * sd.lens_stride_a + (size_t)s * sd.lens_stride_s], 0), max_dim);
+  int off = sd.offs[(size_t)a * sd.offs_stride_a + (size_t)s * sd.offs_stride_s];
+  if (off < 0 || (int64_t)off + len > sd.flat_stride) { len = 0; off = 0; }   // never read outside the arena row
   const T* src = reinterpret_cast<const T*>(sd.flat) + (size_t)a * sd.flat_stride + off;
   T* dst = dense + ((size_t)a * n_tok + s) * max_dim;
   for (int i = lane; i < max_dim; i += 32) dst[i] = i < len ? src[i] : from_f32<T>(0.f);
@@ -252,7 +251,7 @@ extern "C" int dkv_append_decode(const dkv_append_args* a) {
 #define LAUNCH(T)                                                             \
   do {                                                                        \
     if (proj) append_project_kernel<T><<<a->batch, 32 * wpi * items, 0, st>>>(*a, wpi); \
-    else append_decode_kernel<T, false><<<a->batch, threads, 0, st>>>(*a);    \
+    else append_decode_kernel<T><<<a->batch, threads, 0, st>>>(*a);    \
   } while (0)
   if (a->dtype == DKV_F32) LAUNCH(float);
   else if (a->dtype == DKV_F16) LAUNCH(__half);

@@ -90,6 +90,14 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// Device-side routing: true when batch row b (already mapped through batch_index) does not take part in this call.
+__device__ __forceinline__ bool row_routed_out(const dkv_attn_args& p, int b) {
+  if (p.route_min_tokens <= 0 && p.route_max_tokens <= 0) return false;
+  int s = p.seq_len;
+  if (p.seq_lens) s = min(s, max(p.seq_lens[b], 0));
+  return s < p.route_min_tokens || (p.route_max_tokens > 0 && s >= p.route_max_tokens);
+}
+
 __device__ __forceinline__ void set_status(int32_t* status, int32_t bit) {
   if (status != nullptr) atomicOr(status, bit);
 }

@@ -42,6 +42,7 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
   const int A = p.arenas_per_batch, Hq = p.n_q_heads, R = p.rank;
   const int g = h / (Hq / p.n_basis_groups);
   const int a = b * A + (h * A) / Hq;
+  if (MODE == MODE_ATTN && row_routed_out(p, b)) return;   // the row belongs to the other kernel
   int S = p.seq_len;
   if (p.seq_lens) S = min(S, max(p.seq_lens[b], 0));
   int t_begin = 0, t_end = S;
@@ -77,11 +78,19 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
           lk = p.k.lens[(size_t)a * p.k.lens_stride_a + (size_t)s * p.k.lens_stride_s];
           ok = p.k.offs[(size_t)a * p.k.offs_stride_a + (size_t)s * p.k.offs_stride_s];
           lk = min(max(lk, 0), R);
+          if (ok < 0 || (int64_t)ok + lk > p.k.flat_stride) {   // would read outside the arena row: dropped, flagged
+            set_status(p.status, DKV_ST_BAD_LENGTH);
+            lk = 0; ok = 0;
+          }
         }
         if (MODE != MODE_SCORES) {
           lv = p.v.lens[(size_t)a * p.v.lens_stride_a + (size_t)s * p.v.lens_stride_s];
           ov = p.v.offs[(size_t)a * p.v.offs_stride_a + (size_t)s * p.v.offs_stride_s];
           lv = min(max(lv, 0), R);
+          if (ov < 0 || (int64_t)ov + lv > p.v.flat_stride) {
+            set_status(p.status, DKV_ST_BAD_LENGTH);
+            lv = 0; ov = 0;
+          }
         }
       }
       lenk_s[tid] = lk; offk_s[tid] = ok; lenv_s[tid] = lv; offv_s[tid] = ov;

@@ -281,6 +281,7 @@ struct Pack<__half> {
 // Token space of one KV head: batch rows back to back, each rounded up to whole 128-token tiles.
 __device__ __forceinline__ int row_tokens(const dkv_attn_args& p, int i) {
   const int b = p.batch_index ? p.batch_index[i] : i;
+  if (row_routed_out(p, b)) return 0;   // a row routed to the other kernel contributes no tiles
   int s = p.seq_len;
   if (p.seq_lens) s = min(s, max(p.seq_lens[b], 0));
   return s;
@@ -426,7 +427,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   const int n_stages = u_end - u_begin;
   bool project = FUSED;   // fused path: the block projects its row at the end
 
-  if (FUSED && n_stages <= 0) {
+  if (FUSED && n_stages <= 0 && row_routed_out(p, p.batch_index ? p.batch_index[blockIdx.x] : (int)blockIdx.x)) {
+    project = false;   // this row belongs to the other kernel: nothing is written
+  } else if (FUSED && n_stages <= 0) {
     // row without tokens: zeros, flagged
     for (int e = tid; e < G * D; e += NTHREADS) {
       const int b = p.batch_index ? p.batch_index[blockIdx.x] : blockIdx.x;
@@ -929,6 +932,7 @@ __global__ void __launch_bounds__(128) split_combine_kernel(dkv_attn_args p) {
   const WsHeader* wh = reinterpret_cast<const WsHeader*>(p.workspace);
   const float* ws = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(p.workspace) + ws_header_bytes());
   const int i = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (row_routed_out(p, p.batch_index ? p.batch_index[i] : i)) return;   // the row belongs to the other kernel
   const int G = p.n_q_heads / p.n_basis_groups, g = h / G, hl = h - g * G, R = p.rank;
   const int n_cta = wh->n_cta, total_units = wh->total_units;
   const int u_lo = wh->prefix[i], u_hi = wh->prefix[i + 1];

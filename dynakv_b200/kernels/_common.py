@@ -61,7 +61,8 @@ def arena_rows(t: torch.Tensor, what: str) -> torch.Tensor:
 
 
 def build_attn_args(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta, *, out, seq_lens=None,
-                    batch_index=None, k_norm_weight=None, k_norm_eps=1e-6, len_multiple=1, need_workspace=False):
+                    batch_index=None, k_norm_weight=None, k_norm_eps=1e-6, len_multiple=1, need_workspace=False,
+                    route_min_tokens=0, route_max_tokens=0):
     """Fill a dkv_attn_args from torch tensors; returns (args, keepalive)."""
     lib = _lib.load()
     _lib.require_cuda(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, out)
@@ -126,6 +127,9 @@ def build_attn_args(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta, *,
     a.k_norm_eps = float(k_norm_eps)
     a.theta = float(theta)
     a.len_multiple = int(len_multiple)
+    a.route_min_tokens, a.route_max_tokens = int(route_min_tokens), int(route_max_tokens)
+    if (a.route_min_tokens or a.route_max_tokens) and seq_lens is None:
+        raise ValueError("device-side routing needs seq_lens (one cache length per batch row on the device)")
     a.out, a.out_stride_b, a.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
     st = status_word(dev)
     a.status = st.data_ptr()

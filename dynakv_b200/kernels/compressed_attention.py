@@ -108,14 +108,17 @@ class CompressedDecodeLayer:
         _lib.check(_lib.load().dkv_append_decode(C.byref(a)), "dkv_append_decode")
 
     def attend(self, cache: CustomDynamicCache, q: torch.Tensor, out: torch.Tensor, row_counter: torch.Tensor,
-               seq_columns: int, route: str, batch_index: Optional[torch.Tensor] = None,
+               seq_columns: int, route: str, route_min_tokens: int = 0, route_max_tokens: int = 0,
                prepare_only: bool = False) -> None:
+        """Attention of all batch rows through one kernel (``route``); with routing bounds the kernel skips the rows
+        whose current length (read from ``row_counter`` on the device) belongs to the other kernel."""
         ck, cv = cache.key_cache_sp[self.layer_idx], cache.value_cache_sp[self.layer_idx]
         args, keep = build_attn_args(
             q, ck[0], self.k_up, cv[0], self.v_up, ck[1][:, :seq_columns], ck[2][:, :seq_columns],
             cv[1][:, :seq_columns], cv[2][:, :seq_columns], self.theta, out=out, seq_lens=row_counter,
-            batch_index=batch_index, k_norm_weight=self.k_norm_weight, k_norm_eps=self.k_norm_eps,
-            len_multiple=cache.len_multiple, need_workspace=(route == "long_two_stage"))
+            k_norm_weight=self.k_norm_weight, k_norm_eps=self.k_norm_eps,
+            len_multiple=cache.len_multiple, need_workspace=(route == "long_two_stage"),
+            route_min_tokens=route_min_tokens, route_max_tokens=route_max_tokens)
         lib = _lib.load()
         if prepare_only:     # only size and allocate what the call needs (workspace, status word)
             return
@@ -130,13 +133,16 @@ class DecodeGraph:
     """CUDA-graph replay of append + routed attention over a stack of layers.
 
     The caches must have been filled (prefill) with ``token_counts`` so that every layer owns a device
-    row counter; the graph reads the current cache lengths from those counters, so one capture serves
-    every later step as long as no row crosses ``seq_capacity`` or the policy's switch point
-    (re-capture then; ``routes`` fixes which rows run which kernel).
+    row counter; the graph reads the current cache lengths from those counters and the kernels route every
+    row on its own length (``KernelPolicy.switch_tokens``) on the device, so one capture serves every later
+    step -- also when a row crosses the switch point -- as long as no row outgrows ``seq_capacity``.
+    ``horizon`` = number of steps the capture must stay valid for (default: until the cache is full); it only
+    decides whether the long-cache kernels have to be in the graph at all.
     """
 
     def __init__(self, layers: Sequence[CompressedDecodeLayer], cache: CustomDynamicCache, batch: int,
-                 n_q_heads: int, dtype: torch.dtype, device, seq_lens_host: Sequence[int]):
+                 n_q_heads: int, dtype: torch.dtype, device, seq_lens_host: Sequence[int],
+                 horizon: Optional[int] = None):
         self.layers, self.cache = list(layers), cache
         self.batch, self.device = batch, torch.device(device)
         L, Hkv = len(self.layers), cache.arenas_per_batch
@@ -146,11 +152,14 @@ class DecodeGraph:
         self.len_k = torch.full((L, batch, Hkv), 8, dtype=torch.int32, device=device)
         self.len_v = torch.full_like(self.len_k, 8)
         self.out = torch.zeros((L, batch, n_q_heads, 128), dtype=dtype, device=device)
-        short, long_ = self.layers[0].policy.partition(seq_lens_host)
-        self._short = torch.tensor(short, dtype=torch.int32, device=device) if short and long_ else None
-        self._long = torch.tensor(long_, dtype=torch.int32, device=device) if short and long_ else None
-        self._has_short, self._has_long = bool(short), bool(long_)
-        self.kernel_launches_per_step = L * (1 + (1 if short else 0) + (2 if long_ else 0))
+        switch = self.layers[0].policy.switch_tokens
+        cap = cache.key_cache_sp[self.layers[0].layer_idx][1].shape[1]
+        reach = cap if horizon is None else min(cap, max(seq_lens_host) + 1 + int(horizon))
+        # rows only grow: a row is short now or never, and long at some step of the horizon or never
+        self._has_short = any(int(n) + 1 < switch for n in seq_lens_host)
+        self._has_long = reach >= switch
+        self._switch = switch
+        self.kernel_launches_per_step = L * (1 + (1 if self._has_short else 0) + (2 if self._has_long else 0))
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         status_word(self.device)
         self._run_layers(prepare_only=True)   # allocate the split workspace before any capture
@@ -164,10 +173,13 @@ class DecodeGraph:
             cap = ck[1].shape[1]
             if not prepare_only:
                 layer.append(self.cache, self.new_k[li], self.new_v[li], self.len_k[li], self.len_v[li], counter, cap)
+            both = self._has_short and self._has_long
             if self._has_short:
-                layer.attend(self.cache, self.q[li], self.out[li], counter, cap, "short_fused", self._short, prepare_only)
+                layer.attend(self.cache, self.q[li], self.out[li], counter, cap, "short_fused",
+                             route_max_tokens=self._switch if both else 0, prepare_only=prepare_only)
             if self._has_long:
-                layer.attend(self.cache, self.q[li], self.out[li], counter, cap, "long_two_stage", self._long, prepare_only)
+                layer.attend(self.cache, self.q[li], self.out[li], counter, cap, "long_two_stage",
+                             route_min_tokens=self._switch if both else 0, prepare_only=prepare_only)
 
     def capture(self) -> None:
         """Capture one decode step.  Nothing is executed: the cache is left as it is."""

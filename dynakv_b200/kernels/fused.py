@@ -18,7 +18,8 @@ def fused_attention_dispatch(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, 
                              seq_lens: Optional[torch.Tensor] = None,
                              batch_index: Optional[torch.Tensor] = None,
                              k_norm_weight: Optional[torch.Tensor] = None, k_norm_eps: float = 1e-6,
-                             len_multiple: int = 1, out: Optional[torch.Tensor] = None):
+                             len_multiple: int = 1, out: Optional[torch.Tensor] = None,
+                             route_min_tokens: int = 0, route_max_tokens: int = 0):
     """q [B,Hq,1,D] or [B,Hq,D] (already rotated); flat buffers [B,cap] (joint latent rows, as in the
     reference) or [B*Hkv,cap] / [B,Hkv,cap] (per-KV-head arenas); bases [Hkv or Hq, R, D];
     lengths/offsets int32 [rows, S] views.  Returns [B, Hq, D] in q's dtype.
@@ -31,7 +32,8 @@ def fused_attention_dispatch(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, 
         out = torch.empty((q3.shape[0], q3.shape[1], q3.shape[2]), dtype=q3.dtype, device=q3.device)
     args, keep = build_attn_args(q3, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta, out=out,
                                  seq_lens=seq_lens, batch_index=batch_index, k_norm_weight=k_norm_weight,
-                                 k_norm_eps=k_norm_eps, len_multiple=len_multiple)
+                                 k_norm_eps=k_norm_eps, len_multiple=len_multiple, route_min_tokens=route_min_tokens,
+                                 route_max_tokens=route_max_tokens)
     _lib.check(_lib.load().dkv_fused_decode(C.byref(args)), "dkv_fused_decode")
     del keep
     return out

@@ -1,9 +1,13 @@
 """Runtime routing between the short (fused) and long (split two-stage) decode kernels.
 
 Mirrors src/dynakv/kernels/router.py of the reference: ``KernelPolicy(switch_tokens=500)`` and the
-keyword-only ``compressed_decode_attention``.  Extension: with ``seq_lens_host`` (one cache length
-per batch row) every sequence is routed on its own length, so a ragged batch that straddles the
-switch point runs the fused kernel on its short rows and the split kernels on its long rows.
+keyword-only ``compressed_decode_attention``.  Extension: with ``seq_lens`` (one cache length per batch
+row, on the device) every sequence is routed on its own length *by the kernels themselves*: both kernels
+are launched over the whole batch with the policy's switch point as a bound, each skips the rows that
+belong to the other, and nothing is copied to or from the host -- so a ragged batch that straddles the
+switch point, or a row that crosses it between two steps of a captured graph, is handled without
+re-partitioning.  ``seq_lens_host`` (the same lengths as python ints) only lets the call skip a kernel
+that has no row to process.
 """
 from __future__ import annotations
 
@@ -49,20 +53,22 @@ def compressed_decode_attention(
     policy = policy or KernelPolicy()
     common = dict(k_norm_weight=k_norm_weight, k_norm_eps=k_norm_eps, len_multiple=len_multiple, seq_lens=seq_lens)
     args = (q, k_flat, k_up, v_flat, v_up, key_lengths, key_offsets, value_lengths, value_offsets, theta)
-    if seq_lens_host is None:
+    if seq_lens is None:
+        if seq_lens_host is not None:
+            raise ValueError("seq_lens_host needs the matching device tensor seq_lens")
         if policy.select(cache_length) == "short_fused":
             return fused_attention_dispatch(*args, **common)
         return two_stage_attention(*args, **common)
 
-    if seq_lens is None:
-        raise ValueError("seq_lens_host needs the matching device tensor seq_lens")
-    short, long_ = policy.partition(seq_lens_host)
+    # per-row routing on the device
     q3 = q.squeeze(2) if q.dim() == 4 else q
     out = torch.empty((q3.shape[0], q3.shape[1], q3.shape[2]), dtype=q3.dtype, device=q3.device)
-    if short:
-        idx = torch.tensor(short, dtype=torch.int32, device=q3.device) if long_ else None
-        fused_attention_dispatch(*args, out=out, batch_index=idx, **common)
-    if long_:
-        idx = torch.tensor(long_, dtype=torch.int32, device=q3.device) if short else None
-        two_stage_attention(*args, out=out, batch_index=idx, **common)
+    any_short, any_long = True, True
+    if seq_lens_host is not None:
+        short, long_ = policy.partition(seq_lens_host)
+        any_short, any_long = bool(short), bool(long_)
+    if any_short:
+        fused_attention_dispatch(*args, out=out, route_max_tokens=policy.switch_tokens if any_long else 0, **common)
+    if any_long:
+        two_stage_attention(*args, out=out, route_min_tokens=policy.switch_tokens if any_short else 0, **common)
     return out

@@ -19,14 +19,16 @@ from ._common import build_attn_args
 def two_stage_attention(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta, *,
                         seq_lens: Optional[torch.Tensor] = None, batch_index: Optional[torch.Tensor] = None,
                         k_norm_weight: Optional[torch.Tensor] = None, k_norm_eps: float = 1e-6,
-                        len_multiple: int = 1, out: Optional[torch.Tensor] = None):
+                        len_multiple: int = 1, out: Optional[torch.Tensor] = None,
+                        route_min_tokens: int = 0, route_max_tokens: int = 0):
     """Same arguments and result as ``fused_attention_dispatch``; split-KV execution."""
     q3 = q.squeeze(2) if q.dim() == 4 else q
     if out is None:
         out = torch.empty((q3.shape[0], q3.shape[1], q3.shape[2]), dtype=q3.dtype, device=q3.device)
     args, keep = build_attn_args(q3, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta, out=out,
                                  seq_lens=seq_lens, batch_index=batch_index, k_norm_weight=k_norm_weight,
-                                 k_norm_eps=k_norm_eps, len_multiple=len_multiple, need_workspace=True)
+                                 k_norm_eps=k_norm_eps, len_multiple=len_multiple, need_workspace=True,
+                                 route_min_tokens=route_min_tokens, route_max_tokens=route_max_tokens)
     _lib.check(_lib.load().dkv_two_stage_decode(C.byref(args)), "dkv_two_stage_decode")
     del keep
     return out

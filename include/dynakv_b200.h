@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define DKV_VERSION 1
+#define DKV_VERSION 2
 
 /* element types of cache payload, bases, queries and outputs */
 enum { DKV_F32 = 0, DKV_F16 = 1, DKV_BF16 = 2 };
@@ -96,6 +96,13 @@ typedef struct dkv_attn_args {
   int32_t* status;          /* optional device status word (OR-ed into) */
   int32_t n_sm;             /* SM count of the device, for grid sizing; 0 = query */
   void* stream;             /* cudaStream_t */
+  /* Device-side routing (KernelPolicy.select per row, src/dynakv/kernels/router.py:8-17, evaluated on the GPU so
+   * that a captured graph keeps routing correctly while sequences grow): a batch row takes part in this call only
+   * if  route_min_tokens <= tokens(row)  and ( route_max_tokens == 0 or tokens(row) < route_max_tokens ), with
+   * tokens(row) = min(seq_len, seq_lens[row]).  Rows outside are skipped: nothing is written for them and they
+   * raise no status bit.  Both 0 = every row (the default). */
+  int32_t route_min_tokens;
+  int32_t route_max_tokens;
 } dkv_attn_args;
 
 /* Short-cache path: one launch that reconstructs K, applies RoPE, runs QK, online softmax and V.

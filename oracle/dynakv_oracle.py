@@ -120,6 +120,19 @@ def decompress(flat: np.ndarray, lens: np.ndarray, max_dim: int, offs: Optional[
     return out
 
 
+def decompress_gather(flat: np.ndarray, lens: np.ndarray, offs: np.ndarray, max_dim: int) -> np.ndarray:
+    """Same result as ``decompress(flat, lens, max_dim, offs)`` with whole-array numpy indexing, for caches of
+    hundreds of thousands of tokens where the per-token loop above takes minutes (checked against it in
+    tests/test_oracle_golden.py).  compressed_cache.py:36-56 / fused.py:86."""
+    n_rows, s = lens.shape
+    ln = np.minimum(lens.astype(np.int64), max_dim)
+    idx = offs.astype(np.int64)[:, :, None] + np.arange(max_dim, dtype=np.int64)[None, None, :]
+    keep = np.arange(max_dim)[None, None, :] < ln[:, :, None]
+    idx = np.where(keep, idx, 0)
+    rows = np.arange(n_rows)[:, None, None]
+    return np.where(keep, flat[rows, idx], np.zeros((), dtype=flat.dtype))
+
+
 # --------------------------------------------------------------------------
 # RoPE (fused.py:65-66, 97-102; two_stage.py:28-46; custom_attn.py:21-25)
 # --------------------------------------------------------------------------

@@ -99,6 +99,15 @@ def test_16bit_tensor_core_path_on_fixtures(name, fn, dtype):
     _check16(_run(fn, t, float(g["theta"]), len_multiple=1), ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("fn", [fused_attention_dispatch, two_stage_attention])
+def test_16bit_joint_layout_of_the_reference(fn, dtype):
+    # the reference's own layout in 16 bit: one latent row shared by all heads, bases [Hq, R, D], any integer length
+    g, t = _golden_attn("attn_joint_s37", dtype)
+    ref = _oracle(t, float(g["theta"]))
+    _check16(_run(fn, t, float(g["theta"])), ref)
+
+
 @pytest.mark.parametrize("fn", [fused_attention_dispatch, two_stage_attention])
 def test_qwen_knorm_bf16(fn):
     g, t = _golden_attn("attn_qwen_knorm_s50", torch.bfloat16)
@@ -303,9 +312,9 @@ def test_full_rank_and_minimum_rank_rows():
 
 
 def test_split_and_fused_agree_at_full_config2_size_per_sequence():
-    # one sequence of the long-cache configuration at its real length; the oracle would take minutes here,
-    # so the check is the size-independent one: both execution strategies compute the same attention,
-    # and attention is invariant to which split a token lands in.
+    # one sequence of the long-cache configuration at its real length: the two execution strategies compute the same
+    # attention, whichever split a token lands in (the comparison with the oracle at this size is in
+    # tests/test_gpu_decode_step.py)
     case = synthetic.make_layer_case(2117, [32768], "beta:2,8", 500000.0, torch.bfloat16, DEV)
     a = two_stage_attention(*_case_args(case), len_multiple=8).float()
     b = fused_attention_dispatch(*_case_args(case), len_multiple=8).float()

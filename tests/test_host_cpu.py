@@ -46,7 +46,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/dynakv_b200.h but not exported"
     assert declared == set(_lib.EXPORTS)
-    assert lib.dkv_version() == 1
+    assert lib.dkv_version() == 2
 
 
 def test_struct_sizes_match_the_c_layout():
@@ -83,3 +83,23 @@ def test_two_stage_wrappers_require_offsets():
         abx_sparse(torch.zeros(1, 4, 128), torch.zeros(4, 8, 128), torch.zeros(1, 8), torch.zeros(1, 1, dtype=torch.int32))
     with pytest.raises(ValueError):
         avx(torch.zeros(1, 4, 1), torch.zeros(1, 8), torch.zeros(4, 8, 128), torch.zeros(1, 1, dtype=torch.int32))
+
+
+def test_merge_basis_layout_matches_the_reference_rule():
+    # reference: B[h, r, dd] = up[h*head_dim + dd, r] (kernels/compressed_attention.py:278-286, before the
+    # repeat_interleave over query heads, which the kernels replace by head sharing)
+    import torch
+    from dynakv_b200.kernels.compressed_attention import merge_basis
+    n_kv, d, rank = 3, 4, 12
+    up = torch.arange(n_kv * d * rank, dtype=torch.float32).reshape(n_kv * d, rank)
+    b = merge_basis(up, n_kv, d)
+    assert b.shape == (n_kv, rank, d) and b.is_contiguous()
+    for h in range(n_kv):
+        for r in range(rank):
+            for dd in range(d):
+                assert b[h, r, dd] == up[h * d + dd, r]
+    # the reference builds the same tensor as view -> transpose -> (repeat_interleave): compare with that recipe
+    ref = up.view(n_kv, d, rank).transpose(1, 2)
+    assert torch.equal(b, ref)
+    low = merge_basis(up, n_kv, d, low_rank=5)
+    assert torch.equal(low, ref[:, :5])

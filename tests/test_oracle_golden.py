@@ -88,3 +88,12 @@ def test_router_boundary():
     assert O.select_path(128, 128) == "long_two_stage"
     with pytest.raises(ValueError):
         O.select_path(-1)
+
+
+def test_decompress_gather_equals_the_per_token_loop():
+    rng = np.random.default_rng(3)
+    lens = (rng.integers(0, 17, size=(5, 37)) * 8).astype(np.int32)
+    offs = (np.cumsum(lens, axis=1) - lens).astype(np.int32)
+    flat = rng.standard_normal((5, int(lens.sum(axis=1).max()) + 3)).astype(np.float32)
+    assert np.array_equal(O.decompress_gather(flat, lens, offs, 128), O.decompress(flat, lens, 128, offs))
+    assert np.array_equal(O.decompress_gather(flat, lens, offs, 64), O.decompress(flat, lens, 64, offs))

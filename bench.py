@@ -11,15 +11,25 @@ cutoff head) and run the split two-stage decode attention.  The whole step is re
 graph.  ``value`` is tokens/s over all GPUs with the step inputs already in HBM; ``e2e`` is the same
 step driven from pinned host buffers (H2D of q / new K,V rows / cutoffs, D2H of the attention outputs
 inside the timed region).  Each GPU reads ~8 GB of distinct cache bytes per step, far more than L2,
-so no L2 flush is needed between steps.
+so no L2 flush is needed between steps.  After the timed region one (layer, sequence) of the last
+step's output is checked against the CPU oracle (``parity``).
 
 Multi-GPU: the batch is sharded by sequence (one process per GPU, 8 sequences each, no collective in
 the data path) -> weak scaling.  Timing: CUDA events on the launching stream, barrier + synchronize on
-both sides, max over ranks.
+both sides, max over ranks.  Two more legs run at every N and are reported as extra objects:
+``ragged_strong`` -- the ragged-batch configuration (64 sequences, lengths log-uniform in [128, 32768],
+Qwen3 K-RMSNorm, ~48 % retention, per-row routing across the switch point) with the FIXED set of 64
+sequences split over the ranks by a token-balanced partition (strong scaling, no collective); and, for
+N > 1, ``kv_head_sharded`` -- one 32768-token sequence with its 8 KV heads split over the ranks, the
+attention output feeding a row-parallel o_proj summed by one NCCL all-reduce, checked against the
+unsharded result.
 
-``--impl reference`` times the reference's own CPU implementation of the same math (fp32 compact
-masked-dimension attention on dense zero-masked latents, as restated in oracle/) on the host cores,
-rank 0 only, on a bounded sample: one sequence of the workload, one layer per step.
+At N = 1 the line also carries ``cpu_baseline`` (the oracle's restatement of the reference's fp32
+research math on the host cores) and ``gpu_reference`` (the reference's own Triton kernels, JIT-compiled
+for this GPU from the copy installed under baseline/_ref, timed on the same cache tensors).
+
+``--impl reference`` times the reference's own CPU implementation of the same math on the host cores,
+rank 0 only; a step there is a bounded sample of the workload: one sequence x one layer.
 """
 from __future__ import annotations
 
@@ -47,9 +57,10 @@ WORKLOADS = {
 }
 N_Q_HEADS, N_KV_HEADS, HEAD_DIM = 32, 8, 128
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one split-kernel launch divided by its algorithmic bytes,
-# from the ncu capture summarised under profiles/; None until such a capture exists.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.18   # dram read+write / algorithmic bytes, profile_b2_s32768 capture
+# DRAM bytes (read + write) of one split-kernel launch divided by its algorithmic bytes, as counted by ncu on the
+# profile_b2_s32768 workload (the excess is the int32 lens/offs metadata)
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.18
+RAGGED = dict(n_seq=64, lo=128, hi=32768, dist="beta:2.4,2.6", theta=1000000.0, layers=4, seed=3017)
 
 
 def measured_peak():
@@ -107,6 +118,17 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def workload_config(name, w, world, retention=None, bytes_step=None):
+    cfg = {"workload": name, "batch_per_gpu": w["batch"], "cache_len": w["seq"], "layers": w["layers"],
+           "q_heads": N_Q_HEADS, "kv_heads": N_KV_HEADS, "head_dim": HEAD_DIM, "length_dist": w["dist"],
+           "parallelism": "sequence-sharded x%d" % world}
+    if retention is not None:
+        cfg["retention"] = retention
+    if bytes_step is not None:
+        cfg["l2"] = "inputs larger than L2 (%.1f GB of distinct cache bytes per step per GPU), no flush" % (bytes_step / 1e9)
+    return cfg
+
+
 # ------------------------------------------------------------------------------------------ our arm
 def build_workload(w, device, dtype=torch.bfloat16, extra_tokens=64):
     from dynakv_b200 import synthetic
@@ -149,6 +171,172 @@ def fill_step_inputs(graph, w, seed, device=None):
     return host
 
 
+
+def oracle_row(cache, layer_idx, q_row, k_up, v_up, theta, row, n_tokens, k_norm_weight=None):
+    """fp32 compact attention of one batch row from the cache as it is on the GPU (checker, CPU)."""
+    from oracle import dynakv_oracle as O
+    ck, cv = cache.key_cache_sp[layer_idx], cache.value_cache_sp[layer_idx]
+    sl = slice(row * N_KV_HEADS, (row + 1) * N_KV_HEADS)
+    S = int(n_tokens)
+    lk, ok = ck[1][sl, :S].cpu().numpy(), ck[2][sl, :S].cpu().numpy()
+    lv, ov = cv[1][sl, :S].cpu().numpy(), cv[2][sl, :S].cpu().numpy()
+    fk = ck[0][sl, : int((ok + lk).max())].float().cpu().numpy()
+    fv = cv[0][sl, : int((ov + lv).max())].float().cpu().numpy()
+    xk = torch.from_numpy(O.decompress_gather(fk, lk, ok, 128)).view(1, N_KV_HEADS, S, 128)
+    xv = torch.from_numpy(O.decompress_gather(fv, lv, ov, 128)).view(1, N_KV_HEADS, S, 128)
+    valid = torch.from_numpy(lk > 0).view(1, N_KV_HEADS, S)
+    return O.compact_attention_dense(q_row.float().cpu().view(1, N_Q_HEADS, HEAD_DIM), xk, xv, k_up.float().cpu(),
+                                     v_up.float().cpu(), theta, valid, k_norm_weight=k_norm_weight)[0]
+
+
+def parity_of_last_step(graph, cache, w):
+    """Layer 0, sequence 0 of the step that ran last, against the oracle on the cache contents it left."""
+    n = int(cache.seq_lens(0)[0].item())
+    layer = graph.layers[0]
+    ref = oracle_row(cache, 0, graph.q[0][0], layer.k_up, layer.v_up, w["theta"], 0, n)
+    got = graph.out[0][0].float().cpu()
+    return {"max_abs": float((got - ref).abs().max()), "mean_rel": float((got - ref).abs().mean() / ref.abs().mean()),
+            "checked": "layer 0, sequence 0 of the last step (%d tokens) against the CPU oracle" % n,
+            "tolerance": {"max_abs": 2e-2, "mean_rel": 1e-2}}
+
+
+def ragged_strong_leg(dev, world, rank, steps, warmup, timed, dist):
+    """The ragged-batch configuration with a fixed set of sequences split over the ranks (strong scaling)."""
+    from dynakv_b200 import sharding, synthetic
+    from dynakv_b200.kernels.compressed_attention import CompressedDecodeLayer, DecodeGraph
+    from dynakv_b200.kernels.compressed_cache import CustomDynamicCache
+    r = RAGGED
+    lengths = synthetic.log_uniform_lengths(r["n_seq"], r["lo"], r["hi"], seed=r["seed"])
+    parts = sharding.balanced_sequence_partition(lengths, world)
+    mine = parts[rank]
+    tokens_rank = [sum(lengths[i] for i in p) for p in parts]
+    cache = CustomDynamicCache(arenas_per_batch=N_KV_HEADS, len_multiple=8)
+    layers, comp = [], 0
+    knw = 1.0 + 0.02 * torch.randn(128, generator=torch.Generator().manual_seed(3))
+    my_lens = [lengths[i] for i in mine]
+    if mine:
+        for li in range(r["layers"]):
+            case = synthetic.make_layer_case(r["seed"] + 31 * li + 7919 * rank, my_lens, r["dist"], r["theta"], torch.bfloat16,
+                                             dev, N_Q_HEADS, N_KV_HEADS, extra_tokens=2 * (steps + warmup) + 8)
+            cache.adopt(li, (case.k.flat, case.k.lens, case.k.offs, case.k.ptr),
+                        (case.v.flat, case.v.lens, case.v.offs, case.v.ptr), my_lens)
+            comp += case.compressed_bytes()
+            layers.append(CompressedDecodeLayer(li, case.k_up, case.v_up, r["theta"], k_norm_weight=knw))
+        graph = DecodeGraph(layers, cache, len(mine), N_Q_HEADS, torch.bfloat16, dev, my_lens)
+        gen = torch.Generator().manual_seed(17 + rank)
+        graph.q.copy_(torch.randn(graph.q.shape, generator=gen).to(torch.bfloat16))
+        graph.new_k.copy_((torch.randn(graph.new_k.shape, generator=gen) * 0.5).to(torch.bfloat16))
+        graph.new_v.copy_((torch.randn(graph.new_v.shape, generator=gen) * 0.5).to(torch.bfloat16))
+        graph.len_k.copy_((torch.randint(1, 17, graph.len_k.shape, generator=gen) * 8).to(torch.int32))
+        graph.len_v.copy_((torch.randint(1, 17, graph.len_v.shape, generator=gen) * 8).to(torch.int32))
+        graph.capture()
+        fn = graph.step
+    else:
+        fn = lambda: None
+    for _ in range(max(warmup, 3)):
+        fn()
+    ms = timed(fn, steps)
+    comp_t = torch.tensor([float(comp)], device=dev)
+    if world > 1:
+        dist.all_reduce(comp_t)
+    ms_step = ms / steps
+    out = {"workload": "ragged_b64_loguniform_knorm", "scaling": "strong", "sequences": r["n_seq"], "layers": r["layers"],
+           "length_dist": "log-uniform [%d, %d]" % (r["lo"], r["hi"]), "retention_dist": r["dist"],
+           "tokens_cached_per_rank": tokens_rank, "sequences_per_rank": [len(p) for p in parts],
+           "value": r["n_seq"] / (ms_step * 1e-3), "unit": "tokens/s", "ms_per_step": ms_step,
+           "us_per_layer": ms_step * 1e3 / r["layers"],
+           "hbm_gbs_all_ranks": float(comp_t.item()) / (ms_step * 1e-3) / 1e9,
+           "routing": "per row on the device, KernelPolicy(switch_tokens=500); %d of %d sequences below the switch point"
+                      % (sum(1 for n in lengths if n < 500), r["n_seq"])}
+    del cache, layers
+    torch.cuda.empty_cache()
+    return out
+
+
+def kv_head_sharded_leg(dev, world, rank, steps, timed, dist):
+    """One long sequence with its KV heads split over the ranks; row-parallel o_proj + one NCCL all-reduce."""
+    from dynakv_b200 import sharding, synthetic
+    from dynakv_b200.kernels.two_stage import two_stage_attention
+    if N_KV_HEADS % world:
+        return {"skipped": "KV heads do not divide over %d ranks" % world}
+    S, hidden = 32768, 4096
+    case = synthetic.make_layer_case(5151, [S], "beta:2,8", 500000.0, torch.bfloat16, dev, N_Q_HEADS, N_KV_HEADS)
+    (k_lo, k_hi), (q_lo, q_hi) = sharding.shard_kv_heads(N_KV_HEADS, N_Q_HEADS, world, rank)
+    fk, fv, lk, lv, ok, ov = case.views()
+    w_o = (torch.randn(hidden, N_Q_HEADS * HEAD_DIM, generator=torch.Generator().manual_seed(9)) / 64.0).to(torch.bfloat16).to(dev)
+    sl = slice(k_lo, k_hi)
+    q_loc = case.q[:, q_lo:q_hi].contiguous()
+
+    def local_step():
+        o = two_stage_attention(q_loc, fk[sl], case.k_up[sl].contiguous(), fv[sl], case.v_up[sl].contiguous(), lk[sl], ok[sl],
+                                lv[sl], ov[sl], case.theta, len_multiple=8)
+        return sharding.row_parallel_linear(o.reshape(1, -1), w_o[:, q_lo * HEAD_DIM:q_hi * HEAD_DIM])
+
+    y = local_step()
+    full = two_stage_attention(case.q, fk, case.k_up, fv, case.v_up, lk, ok, lv, ov, case.theta, len_multiple=8)
+    y_ref = full.reshape(1, -1) @ w_o.T
+    err = float((y.float() - y_ref.float()).abs().max())
+    scale = float(y_ref.float().abs().mean())
+    for _ in range(3):
+        local_step()
+    ms = timed(local_step, steps)
+    return {"workload": "one sequence of %d tokens, %d KV heads per rank, o_proj %dx%d row-parallel + all-reduce" %
+                        (S, k_hi - k_lo, hidden, N_Q_HEADS * HEAD_DIM),
+            "us_per_layer_step": ms / steps * 1e3, "max_abs_vs_unsharded": err, "mean_abs_of_reference": scale,
+            "collective": "NCCL all-reduce of [1, %d] bf16" % hidden}
+
+
+def gpu_reference_leg(graph, cache, w, dev):
+    """The reference's own Triton kernels (abx_sparse -> avx, and the fused kernel) on layer 0 of the workload, one call
+    pair per KV head (the reference API with a single basis group is the per-head layout), CUDA-event timed."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "dynakv")):
+        return {"unavailable": "baseline/_ref holds no installed copy of the reference"}
+    try:
+        sys.path.insert(0, ref_root)
+        from dynakv.kernels.two_stage import abx_sparse, avx
+        layer = graph.layers[0]
+        ck, cv = cache.key_cache_sp[0], cache.value_cache_sp[0]
+        B = graph.batch
+        S = int(cache.seq_lens(0).max().item())
+        cap_k, cap_v = ck[0].shape[1], cv[0].shape[1]
+        fk = ck[0].view(B, N_KV_HEADS, cap_k); fv = cv[0].view(B, N_KV_HEADS, cap_v)
+        lk = ck[1].view(B, N_KV_HEADS, -1)[:, :, :S]; ok = ck[2].view(B, N_KV_HEADS, -1)[:, :, :S]
+        lv = cv[1].view(B, N_KV_HEADS, -1)[:, :, :S]; ov = cv[2].view(B, N_KV_HEADS, -1)[:, :, :S]
+        G = N_Q_HEADS // N_KV_HEADS
+        q = graph.q[0]
+
+        def one_layer():
+            outs = []
+            for h in range(N_KV_HEADS):
+                qh = q[:, h * G:(h + 1) * G].contiguous()
+                sc = abx_sparse(qh, layer.k_up[h:h + 1], fk[:, h], lk[:, h], offsets=ok[:, h], theta=w["theta"])
+                outs.append(avx(sc, fv[:, h], layer.v_up[h:h + 1], lv[:, h], ov[:, h]))
+            return torch.cat(outs, dim=1)
+
+        ref_out = one_layer()            # first call compiles and autotunes
+        one_layer()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        e0.record()
+        for _ in range(reps):
+            one_layer()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / reps * 1e3
+        diff = float((ref_out.float() - graph.out[0].float()).abs().max())
+        return {"kernels": "reference abx_sparse + avx (Triton %s, JIT for this GPU), %d per-KV-head call pairs per layer" %
+                           (__import__("triton").__version__, N_KV_HEADS),
+                "us_per_layer": us, "max_abs_vs_ours": diff,
+                "note": "same cache tensors and queries as layer 0 of the last step; scores round-trip HBM in the query dtype"}
+    except Exception as exc:   # the baseline is reported, never required
+        return {"unavailable": "%s: %s" % (type(exc).__name__, str(exc)[:200])}
+    finally:
+        if sys.path and sys.path[0] == ref_root:
+            sys.path.pop(0)
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -189,12 +377,8 @@ def run_ours(args):
             fn()
         e1.record()
         barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        from dynakv_b200.sharding import max_over_ranks
+        return max_over_ranks(e0.elapsed_time(e1), dev)
 
     for _ in range(max(args.warmup, 3)):
         graph.step()
@@ -208,6 +392,7 @@ def run_ours(args):
     ms_e2e = timed(lambda: graph.step_from_host(*host_in, out_host), args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
+    h2d_bytes, d2h_bytes = graph.h2d_bytes_per_step(), graph.d2h_bytes_per_step()
     # dominant kernel: the split decode kernel, timed alone per launch on its stream
     L = len(graph.layers)
     kernel_ms = None
@@ -243,6 +428,19 @@ def run_ours(args):
         torch.cuda.synchronize()
         kernel_ms = e0.elapsed_time(e1) / (reps * len(calls))
     status = _common.read_status(dev)
+    parity = parity_of_last_step(graph, cache, w) if rank == 0 else None
+    gpu_ref = gpu_reference_leg(graph, cache, w, dev) if (rank == 0 and world == 1 and not args.no_gpu_reference) else None
+    L = len(graph.layers)
+    bytes_layer = sum(comp_bytes) / len(comp_bytes)
+    n_launch = graph.kernel_launches_per_step
+    # free the main workload before the extra legs build theirs
+    del graph, cache
+    torch.cuda.empty_cache()
+    ragged = None if args.no_extra_legs else ragged_strong_leg(dev, world, rank, max(2, min(args.steps, 10)), args.warmup, timed, dist)
+    kvsh = None
+    if world > 1 and not args.no_extra_legs:
+        kvsh = kv_head_sharded_leg(dev, world, rank, max(2, min(args.steps, 10)), timed, dist)
+    status |= _common.read_status(dev)
 
     if rank != 0:
         if world > 1:
@@ -250,25 +448,20 @@ def run_ours(args):
         return
     peak, peak_kind = measured_peak()
     ms_step = ms_total / args.steps
-    bytes_layer = sum(comp_bytes) / len(comp_bytes)
     total_tokens = w["batch"] * world
     line = {
         "metric": "decode_attn_tokens_per_s", "value": total_tokens / (ms_step * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": w["batch"], "cache_len": w["seq"], "layers": L,
-                   "q_heads": N_Q_HEADS, "kv_heads": N_KV_HEADS, "head_dim": HEAD_DIM, "length_dist": w["dist"],
-                   "retention": 0.5 * bytes_layer / (sum(seq_lens) * N_KV_HEADS * 128 * 2),
-                   "l2": "inputs larger than L2 (%.1f GB of distinct cache bytes per step per GPU), no flush" %
-                         (sum(comp_bytes) / 1e9),
-                   "parallelism": "sequence-sharded x%d" % world},
+        "config": workload_config(args.workload, w, world, 0.5 * bytes_layer / (sum(seq_lens) * N_KV_HEADS * 128 * 2),
+                                  sum(comp_bytes)),
         "us_per_layer": ms_step * 1e3 / L,
         "hbm_gbs_step": sum(comp_bytes) / (ms_step * 1e-3) / 1e9,
         "e2e": {"value": total_tokens / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": graph.h2d_bytes_per_step(), "d2h_bytes_per_step": graph.d2h_bytes_per_step(),
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                 "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": graph.kernel_launches_per_step * args.steps,
-        "clocks": clocks, "device_status": status,
+        "gpu_launches": n_launch * args.steps,
+        "clocks": clocks, "device_status": status, "parity": parity,
     }
     if kernel_ms is not None:
         achieved = bytes_layer / (kernel_ms * 1e-3) / 1e9
@@ -276,10 +469,17 @@ def run_ours(args):
             "kernel": "mma_decode_kernel<bf16, split>", "bound": "hbm", "achieved": achieved, "peak": peak,
             "peak_source": "of " + peak_kind, "unit": "GB/s", "frac": achieved / peak, "us_per_launch": kernel_ms * 1e3,
             "algorithmic_bytes_per_launch": bytes_layer,
-            "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_layer) if NCU_TRAFFIC_PER_ALGORITHMIC_BYTE else None,
-            "frac_of_nominal_8TBs": achieved / 8000.0}
+            "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_layer,
+            "frac_of_nominal_8TBs": achieved / 8000.0,
+            "us_per_layer_outside_the_kernel": ms_step * 1e3 / L - kernel_ms * 1e3}
+    if ragged is not None:
+        line["ragged_strong"] = ragged
+    if kvsh is not None:
+        line["kv_head_sharded"] = kvsh
+    if gpu_ref is not None:
+        line["gpu_reference"] = gpu_ref
     if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_reference(w, steps=3, warmup=1)
+        line["cpu_baseline"] = cpu_reference(w, steps=20, warmup=2)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -287,36 +487,50 @@ def run_ours(args):
 
 # ------------------------------------------------------------------------------------- reference arm
 def cpu_reference(w, steps, warmup, max_seconds=25.0):
-    """The reference's CPU math (oracle restatement) on one sequence x one layer of the workload."""
+    """The reference's CPU math (oracle restatement of the fp32 research attention) on one sequence x one layer of
+    the workload per pass, all host cores; plus the CPU-runnable configuration (fp32, one sequence of 256 tokens)
+    at one thread and at all threads."""
     from dynakv_b200 import synthetic
     from oracle import dynakv_oracle as O
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     S, L = w["seq"], w["layers"]
-    case = synthetic.make_layer_case(2017, [S], w["dist"], w["theta"], torch.bfloat16, "cpu", N_Q_HEADS, N_KV_HEADS)
-    fk, fv, lk, lv, ok, ov = case.views()
-    xk = torch.from_numpy(O.decompress(fk.float().numpy(), lk.numpy(), 128, ok.numpy())).view(1, N_KV_HEADS, S, 128)
-    xv = torch.from_numpy(O.decompress(fv.float().numpy(), lv.numpy(), 128, ov.numpy())).view(1, N_KV_HEADS, S, 128)
-    q, ku, vu = case.q.float(), case.k_up.float(), case.v_up.float()
-    valid = (lk > 0).view(1, N_KV_HEADS, S)
-    times = []
-    t_start = time.perf_counter()
-    for i in range(warmup + steps):
-        t0 = time.perf_counter()
-        O.compact_attention_dense(q, xk, xv, ku, vu, w["theta"], valid)
-        dt = time.perf_counter() - t0
-        if i >= warmup:
-            times.append(dt)
-        if time.perf_counter() - t_start > max_seconds and len(times) >= 1:
-            break
+
+    def dense_case(seed, seq, dist, theta, dtype):
+        case = synthetic.make_layer_case(seed, [seq], dist, theta, dtype, "cpu", N_Q_HEADS, N_KV_HEADS)
+        fk, fv, lk, lv, ok, ov = case.views()
+        xk = torch.from_numpy(O.decompress_gather(fk.float().numpy(), lk.numpy(), ok.numpy(), 128)).view(1, N_KV_HEADS, seq, 128)
+        xv = torch.from_numpy(O.decompress_gather(fv.float().numpy(), lv.numpy(), ov.numpy(), 128)).view(1, N_KV_HEADS, seq, 128)
+        return case.q.float(), xk, xv, case.k_up.float(), case.v_up.float(), (lk > 0).view(1, N_KV_HEADS, seq)
+
+    def time_passes(inputs, theta, n, n_warm, budget):
+        times, t_start = [], time.perf_counter()
+        for i in range(n_warm + n):
+            t0 = time.perf_counter()
+            O.compact_attention_dense(*inputs[:5], theta, inputs[5])
+            dt = time.perf_counter() - t0
+            if i >= n_warm:
+                times.append(dt)
+            if time.perf_counter() - t_start > budget and len(times) >= 3:
+                break
+        return times
+
+    main = dense_case(2017, S, w["dist"], w["theta"], torch.bfloat16)
+    times = time_passes(main, w["theta"], steps, warmup, max_seconds)
     t_layer_seq = statistics.median(times)
+    small = dense_case(17, 256, "uniform", 500000.0, torch.float32)
+    t_small_all = statistics.median(time_passes(small, 500000.0, 20, 3, 5.0))
+    torch.set_num_threads(1)
+    t_small_one = statistics.median(time_passes(small, 500000.0, 20, 3, 5.0))
+    torch.set_num_threads(threads)
     # a decode step of one sequence is L such layer passes; sequences are independent
     tok_s = 1.0 / (t_layer_seq * L)
     return {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
             "sample": "1 sequence x 1 layer of the workload (cache length %d) per pass, %d timed passes, "
                       "median %.1f ms; value = 1 / (pass time x %d layers)" % (S, len(times), t_layer_seq * 1e3, L),
-            "seconds_per_pass": t_layer_seq}
+            "seconds_per_pass": t_layer_seq, "passes": len(times),
+            "fp32_b1_s256_ms_per_layer": {"threads_1": t_small_one * 1e3, "threads_%d" % threads: t_small_all * 1e3}}
 
 
 def run_reference(args):
@@ -325,14 +539,14 @@ def run_reference(args):
         return
     w = WORKLOADS[args.workload]
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    base = cpu_reference(w, steps=args.steps, warmup=args.warmup, max_seconds=120.0)
-    L = w["layers"]
+    base = cpu_reference(w, steps=max(args.steps, 3), warmup=args.warmup, max_seconds=150.0)
+    # a step of this arm is the bounded sample that actually ran: one sequence x one layer (the reported
+    # ms_per_step times steps is the time spent); value is the whole-workload rate it implies
     line = {
         "impl": "reference", "metric": "decode_attn_tokens_per_s", "value": base["value"], "unit": "tokens/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["seconds_per_pass"] * L * 1e3,
+        "n_gpus": world, "steps": base["passes"], "warmup": args.warmup, "ms_per_step": base["seconds_per_pass"] * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": w["batch"], "cache_len": w["seq"], "layers": L,
-                   "q_heads": N_Q_HEADS, "kv_heads": N_KV_HEADS, "head_dim": HEAD_DIM, "length_dist": w["dist"]},
+        "config": workload_config(args.workload, w, world),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -348,6 +562,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="long_b8_s32768", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-reference", action="store_true", help="skip the reference's Triton kernels at N=1")
+    ap.add_argument("--no-extra-legs", action="store_true", help="skip the ragged strong-scaling and KV-head-sharded legs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -30,6 +30,22 @@ def shard_sequences(n_sequences: int, world_size: int, rank: int) -> Tuple[int, 
     return block_range(n_sequences, world_size, rank)
 
 
+def balanced_sequence_partition(lengths, world_size: int):
+    """Token-balanced assignment of ragged sequences to ranks: longest first, each to the rank with the fewest
+    tokens so far (ties to the lower rank).  Returns one ascending index list per rank; every rank computes the
+    same partition from the same lengths, so nothing is communicated."""
+    if world_size < 1:
+        raise ValueError("world_size must be positive")
+    order = sorted(range(len(lengths)), key=lambda i: (-int(lengths[i]), i))
+    load = [0] * world_size
+    parts = [[] for _ in range(world_size)]
+    for i in order:
+        r = min(range(world_size), key=lambda k: (load[k], k))
+        parts[r].append(i)
+        load[r] += int(lengths[i])
+    return [sorted(p) for p in parts]
+
+
 def shard_kv_heads(n_kv_heads: int, n_q_heads: int, world_size: int, rank: int):
     """Returns ((kv_lo, kv_hi), (q_lo, q_hi)): the rank's KV heads and the query heads that use them."""
     if n_kv_heads % world_size != 0:

@@ -103,3 +103,15 @@ def test_merge_basis_layout_matches_the_reference_rule():
     assert torch.equal(b, ref)
     low = merge_basis(up, n_kv, d, low_rank=5)
     assert torch.equal(low, ref[:, :5])
+
+
+def test_balanced_sequence_partition_covers_every_sequence_and_balances_tokens():
+    from dynakv_b200 import sharding, synthetic
+    lengths = synthetic.log_uniform_lengths(64, 128, 32768, seed=3017)
+    for world in (1, 2, 4, 8):
+        parts = sharding.balanced_sequence_partition(lengths, world)
+        assert sorted(i for p in parts for i in p) == list(range(64))
+        loads = [sum(lengths[i] for i in p) for p in parts]
+        assert max(loads) - min(loads) <= max(lengths)          # longest-first greedy bound
+        assert max(loads) <= 1.25 * sum(lengths) / world or world == 1 or max(lengths) > sum(lengths) / world
+    assert sharding.balanced_sequence_partition([5, 5], 4) == [[0], [1], [], []]

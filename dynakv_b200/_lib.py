@@ -81,6 +81,7 @@ class GateArgs(C.Structure):
         ("x", C.c_void_p), ("x_stride", C.c_int64), ("w", C.c_void_p), ("b", C.c_void_p),
         ("lengths", C.c_void_p), ("masked", C.c_void_p), ("masked_stride", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("stream", C.c_void_p),
+        ("len_multiple", C.c_int32), ("native_rounding", C.c_int32),
     ]
 
 

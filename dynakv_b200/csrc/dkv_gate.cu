@@ -3,7 +3,8 @@
 //   length = #{ i < low_rank : c_{d-1-i} >= threshold }          (the kept set is a prefix: c is non-decreasing)
 // Reference: kv_process_fused, src/dynakv/kernels/compressed_attention.py:84-119 (one side per call; the
 // reference runs K and V rows through one concatenated softmax/cumsum call, which is row-wise anyway).
-// All arithmetic is fp32 whatever the storage type.  Two kernels: the logits (8 rows per CTA, so that W is read
+// Sums are fp32 whatever the storage type; with native_rounding the intermediate tensors are rounded to the storage
+// type where the reference's torch ops materialise them.  Two kernels: the logits (8 rows per CTA, so that W is read
 // once per 8 rows; the reduction is cut in chunks when there are few rows), then one warp per row for the rest.
 #include <math.h>
 
@@ -91,6 +92,8 @@ __global__ void __launch_bounds__(256) gate_count_kernel(dkv_gate_args p, int n_
   const int row = blockIdx.x * 8 + warp;
   if (row >= p.n_rows) return;
   const T* b = reinterpret_cast<const T*>(p.b);
+  const bool native = p.native_rounding != 0 && sizeof(T) == 2;
+  const float thr = native ? to_f32(from_f32<T>(p.threshold)) : p.threshold;   // the comparison converts the scalar
   const float* part = reinterpret_cast<const float*>(p.workspace);
   float* lg = lg_s[warp];
   float mx = -INFINITY;
@@ -112,6 +115,7 @@ __global__ void __launch_bounds__(256) gate_count_kernel(dkv_gate_args p, int n_
 #pragma unroll
         for (int c = 0; c < 8; ++c) v += pv[u][c];
         v += to_f32(b[j]);
+        if (native) v = to_f32(from_f32<T>(v));   // addmm writes the logits in the storage type
         lg[j] = v;
         mx = fmaxf(mx, v);
       }
@@ -129,6 +133,11 @@ __global__ void __launch_bounds__(256) gate_count_kernel(dkv_gate_args p, int n_
   // lane l owns the contiguous columns [l*per, (l+1)*per): local sums, exclusive scan over lanes, then the walk
   const int per = (d + 31) / 32;
   const int j0 = min(lane * per, d), j1 = min(j0 + per, d);
+  if (native) {   // softmax writes the probabilities in the storage type
+    for (int j = lane; j < d; j += 32) lg[j] = to_f32(from_f32<T>(lg[j] / z));
+    z = 1.f;
+    __syncwarp();
+  }
   float local = 0.f;
   for (int j = j0; j < j1; ++j) local += lg[j] / z;
   float incl = local;
@@ -142,10 +151,12 @@ __global__ void __launch_bounds__(256) gate_count_kernel(dkv_gate_args p, int n_
   int cnt = 0;
   for (int j = j0; j < j1; ++j) {
     run += lg[j] / z;
-    if (j >= lo && run >= p.threshold) ++cnt;
+    const float c = native ? to_f32(from_f32<T>(run)) : run;   // cumsum writes every running sum in the storage type
+    if (j >= lo && c >= thr) ++cnt;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if (p.len_multiple > 1) cnt = min((cnt + p.len_multiple - 1) / p.len_multiple * p.len_multiple, d - d % p.len_multiple);
   if (lane == 0) p.lengths[row] = cnt;
   if (p.masked) {
     const T* x = reinterpret_cast<const T*>(p.x);

@@ -28,13 +28,30 @@ def merge_basis(up: torch.Tensor, n_kv_heads: int, head_dim: int, low_rank: Opti
     return up[:, :rank].reshape(n_kv_heads, head_dim, rank).transpose(1, 2).contiguous()
 
 
+_gate_scratch = {}
+
+
+def _scratch(device, n_floats: int) -> torch.Tensor:
+    """Grow-only fp32 scratch per device (reused by every gate call on the current stream)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _gate_scratch.get(key)
+    if buf is None or buf.numel() < n_floats:
+        buf = torch.empty(max(n_floats, 1 << 16), dtype=torch.float32, device=device)
+        _gate_scratch[key] = buf
+    return buf
+
+
 def gate_lengths(states: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, low_rank: int,
-                 threshold: float = 0.1, return_masked: bool = True):
+                 threshold: float = 0.1, return_masked: bool = True, len_multiple: int = 1,
+                 native_rounding: bool = True):
     """Cutoff gate of one side (kernels/compressed_attention.py:84-119, one of the two halves of
     ``kv_process_fused``): ``states`` [..., d] spectral coefficient rows, ``weight`` [d, d], ``bias`` [d] or [1, d].
 
     Returns (masked states or None, lengths int32 [...]): lengths[t] = #{i < low_rank : cumsum(softmax(x W + b))
-    [d-1-i] >= threshold}, masked = states with everything past the length zeroed.  fp32 arithmetic.
+    [d-1-i] >= threshold}, masked = states with everything past the length zeroed.  fp32 sums; for 16-bit inputs
+    ``native_rounding`` rounds the intermediates where the reference's torch ops do, so the lengths are the ones
+    the reference computes in that dtype.  ``len_multiple=8`` rounds each length up to a multiple of 8 (a superset
+    of the gate's choice), the form the tensor-core decode kernels take.
     """
     if not states.is_cuda:
         raise RuntimeError("dynakv_b200 has no CPU path: the gate needs CUDA tensors")
@@ -56,19 +73,21 @@ def gate_lengths(states: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
     a.masked, a.masked_stride = (masked.data_ptr(), masked.stride(0)) if return_masked else (None, 0)
     lib = _lib.load()
     need = lib.dkv_gate_workspace_bytes(C.byref(a))
-    scratch = torch.empty(max(need, 4) // 4, dtype=torch.float32, device=states.device)
+    scratch = _scratch(states.device, max(need, 4) // 4)
     a.workspace, a.workspace_bytes = scratch.data_ptr(), scratch.numel() * 4
+    a.len_multiple, a.native_rounding = int(len_multiple), int(bool(native_rounding))
     a.stream = _lib.stream_ptr(states.device)
     _lib.check(lib.dkv_gate_lengths(C.byref(a)), "dkv_gate_lengths")
     lead = states.shape[:-1]
     return (masked.reshape(*lead, d) if return_masked else None), lengths.reshape(lead)
 
 
-def kv_process_fused(key_states: torch.Tensor, value_states: torch.Tensor, Wk, bk, Wv, bv, low_rank: int):
+def kv_process_fused(key_states: torch.Tensor, value_states: torch.Tensor, Wk, bk, Wv, bv, low_rank: int,
+                     len_multiple: int = 1):
     """Drop-in for the reference module method of the same name (kernels/compressed_attention.py:84-119):
     returns (k_out, v_out, len_k, len_v, 1, 1) for key_states / value_states [B, S, d]."""
-    k_out, len_k = gate_lengths(key_states, Wk, bk, low_rank)
-    v_out, len_v = gate_lengths(value_states, Wv, bv, low_rank)
+    k_out, len_k = gate_lengths(key_states, Wk, bk, low_rank, len_multiple=len_multiple)
+    v_out, len_v = gate_lengths(value_states, Wv, bv, low_rank, len_multiple=len_multiple)
     return k_out, v_out, len_k, len_v, 1, 1
 
 

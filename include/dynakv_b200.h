@@ -202,8 +202,14 @@ int dkv_decompress(int32_t dtype, int32_t n_arena, int32_t n_tok, int32_t max_di
 /* ---- cutoff gate ------------------------------------------------------- */
 /* Kept-coefficient count of token rows: logits = b + x.W, p = softmax(logits), c = cumsum(p),
  * length = #{ i < low_rank : c[dim-1-i] >= threshold } (threshold 0.1 in the reference); optionally the
- * rows with everything past their length zeroed.  fp32 arithmetic for every storage type.
- * Replaces kv_process_fused -- src/dynakv/kernels/compressed_attention.py:84-119 (one side, K or V, per call). */
+ * rows with everything past their length zeroed.
+ * Replaces kv_process_fused -- src/dynakv/kernels/compressed_attention.py:84-119 (one side, K or V, per call).
+ * Arithmetic: sums in fp32.  With native_rounding != 0 and a 16-bit dtype the intermediate tensors are rounded to
+ * that dtype where the reference's torch ops materialise them (logits after addmm, probabilities after softmax,
+ * every running sum after cumsum, and the threshold itself), so that lengths agree with the reference run in the
+ * same dtype; with 0 nothing is rounded (the fp32 result on the stored values).
+ * len_multiple > 1 rounds every length UP to that multiple (capped at dim rounded down to it): the kept set is a
+ * superset of the gate's, in the form the tensor-core decode kernels take (multiples of 8). */
 typedef struct dkv_gate_args {
   int32_t dtype;          /* DKV_F32 / DKV_F16 / DKV_BF16: type of x, w, b, masked */
   int32_t n_rows;         /* token rows */
@@ -220,6 +226,8 @@ typedef struct dkv_gate_args {
   void* workspace;        /* fp32 scratch of dkv_gate_workspace_bytes(args) bytes */
   size_t workspace_bytes;
   void* stream;
+  int32_t len_multiple;   /* 0 or 1: exact counts */
+  int32_t native_rounding;
 } dkv_gate_args;
 size_t dkv_gate_workspace_bytes(const dkv_gate_args* args);
 int dkv_gate_lengths(const dkv_gate_args* args);

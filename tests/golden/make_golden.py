@@ -254,6 +254,34 @@ def gate_fixture(name, seed, n_rows, d):
     print("wrote", name, "len_k", len_k.flatten().tolist()[:8])
 
 
+def gate_inputs(seed, n_rows, d, dtype):
+    """Seeded inputs of the large gate fixtures (the weights are too big to store): K/V coefficient rows with the
+    decaying spectrum of the synthetic caches, gate weights and biases.  Returns (k, v, Wk, bk, Wv, bv) in ``dtype``."""
+    gen = torch.Generator().manual_seed(seed)
+    sigma = torch.exp(-torch.arange(d, dtype=torch.float32) / (d / 4.0))
+    k = torch.randn(n_rows, 1, d, generator=gen) * sigma * 2.0
+    v = torch.randn(n_rows, 1, d, generator=gen) * sigma * 2.0
+    Wk = torch.randn(d, d, generator=gen) * (2.0 / d ** 0.5)
+    Wv = torch.randn(d, d, generator=gen) * (2.0 / d ** 0.5)
+    bk = torch.randn(1, d, generator=gen) + torch.linspace(2.0, -2.0, d)
+    bv = torch.randn(1, d, generator=gen) + torch.linspace(2.0, -2.0, d)
+    return tuple(t.to(dtype) for t in (k, v, Wk, bk, Wv, bv))
+
+
+def gate_seeded_fixture(name, seed, n_rows, d, dtype):
+    """G4 at model width: the reference's kv_process_fused in ``dtype`` on the seeded inputs; only the lengths and
+    a checksum of the inputs are stored."""
+    from dynakv.kernels.compressed_attention import KVProcessor
+    k, v, Wk, bk, Wv, bv = gate_inputs(seed, n_rows, d, dtype)
+    me = types.SimpleNamespace(Wk=Wk, bk=bk, Wv=Wv, bv=bv, low_rank=d)
+    _, _, len_k, len_v, _, _ = KVProcessor.kv_process_fused(me, k, v)
+    chk = np.array([float(t.double().sum()) for t in (k, v, Wk, bk, Wv, bv)])
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), len_k=len_k.numpy().reshape(-1), len_v=len_v.numpy().reshape(-1),
+                        checksum=chk, seed=np.int64(seed), n_rows=np.int64(n_rows), d=np.int64(d),
+                        dtype=np.array(str(dtype).replace("torch.", "")))
+    print("wrote", name, "mean len_k %.1f" % float(len_k.float().mean()), "min", int(len_k.min()), "max", int(len_k.max()))
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py <path to a checkout of the reference project>")
@@ -274,6 +302,8 @@ def main():
     cache_fixture("cache_prefill_decode", seed=21, n_rows=3, R=128, s_prefill=9, n_decode=6, len_step=8)
     cache_fixture("cache_anylen", seed=22, n_rows=2, R=96, s_prefill=5, n_decode=4, len_step=1)
     gate_fixture("gate_d64", seed=31, n_rows=6, d=64)
+    for dt, nm in ((torch.float32, "f32"), (torch.bfloat16, "bf16"), (torch.float16, "f16")):
+        gate_seeded_fixture("gate_d1024_" + nm, seed=41, n_rows=256, d=1024, dtype=dt)
 
 
 if __name__ == "__main__":

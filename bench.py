@@ -286,6 +286,68 @@ def kv_head_sharded_leg(dev, world, rank, steps, timed, dist):
             "collective": "NCCL all-reduce of [1, %d] bf16" % hidden}
 
 
+def prefill_compress_leg(dev, reps=200):
+    """Bulk compression of a prompt block (8 sequences x 8192 tokens x 8 KV heads, bf16): tensor-core projection onto
+    the per-head bases, then the ragged pack; CUDA events, inputs larger than L2."""
+    import ctypes as C
+    from dynakv_b200 import _lib, synthetic
+    from dynakv_b200.kernels.compressed_attention import project_bulk
+    from dynakv_b200.kernels.compressed_cache import CustomDynamicCache
+    B, S = 8, 8192
+    gen = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(B, S, N_KV_HEADS * 128, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    basis = synthetic.qr_bases(N_KV_HEADS, 71, torch.bfloat16, dev)
+    out = torch.empty_like(x)
+    lens = synthetic.draw_lengths((B, N_KV_HEADS, S), "beta:2,5", gen, dev)
+
+    def ev_time(fn, reps):
+        for _ in range(reps // 2):      # long enough for the clocks to settle before the timed launches
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    ms_proj = ev_time(lambda: project_bulk(x, basis, out=out), reps)
+    flops = 2.0 * B * S * N_KV_HEADS * 128 * 128
+    io = 2.0 * x.numel() * 2 + basis.numel() * 2
+    cache = CustomDynamicCache(arenas_per_batch=N_KV_HEADS, len_multiple=8)
+    cache.reserve(0, B, int(lens.sum(dim=2).max().item()) + 64, S + 8, torch.bfloat16, dev)
+    ck = cache.key_cache_sp[0]
+    lens2 = lens.reshape(B * N_KV_HEADS, S).contiguous()
+    p = _lib.PackArgs()
+    p.dtype, p.batch, p.arenas_per_batch, p.n_new, p.max_dim = _lib.DKV_BF16, B, N_KV_HEADS, S, 128
+    p.states, p.stride_b, p.stride_j, p.stride_s = out.data_ptr(), out.stride(0), 128, out.stride(1)
+    p.new_lens, p.side = lens2.data_ptr(), cache._side(ck)
+    p.seq_pos, p.seq_capacity, p.len_multiple = 0, ck[1].shape[1], 8
+    p.stream = _lib.stream_ptr(dev)
+    lib = _lib.load()
+
+    def pack():
+        ck[3].zero_()
+        _lib.check(lib.dkv_pack_bulk(C.byref(p)), "dkv_pack_bulk")
+
+    ms_pack = ev_time(pack, reps)
+    payload = float(lens.sum().item()) * 2
+    peak_tf = None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak_tf = float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        pass
+    hbm, _ = measured_peak()
+    return {"workload": "8 sequences x 8192 prompt tokens x 8 KV heads, bf16",
+            "project_bulk": {"ms": ms_proj, "tflops": flops / (ms_proj * 1e-3) / 1e12, "of_bf16_sustained": None if not peak_tf else flops / (ms_proj * 1e-3) / 1e12 / peak_tf,
+                             "gbs": io / (ms_proj * 1e-3) / 1e9, "of_hbm_peak": io / (ms_proj * 1e-3) / 1e9 / hbm,
+                             "bound": "hbm (44 flop per byte moved)"},
+            "pack_bulk": {"ms": ms_pack, "payload_gbs_read_plus_write": 2 * payload / (ms_pack * 1e-3) / 1e9,
+                          "of_hbm_peak": 2 * payload / (ms_pack * 1e-3) / 1e9 / hbm, "retention": payload / (x.numel() * 2)}}
+
+
 def gpu_reference_leg(graph, cache, w, dev):
     """The reference's own Triton kernels (abx_sparse -> avx, and the fused kernel) on layer 0 of the workload, one call
     pair per KV head (the reference API with a single basis group is the per-head layout), CUDA-event timed."""
@@ -436,6 +498,7 @@ def run_ours(args):
     # free the main workload before the extra legs build theirs
     del graph, cache
     torch.cuda.empty_cache()
+    prefill = prefill_compress_leg(dev) if (rank == 0 and world == 1 and not args.no_extra_legs) else None
     ragged = None if args.no_extra_legs else ragged_strong_leg(dev, world, rank, max(2, min(args.steps, 10)), args.warmup, timed, dist)
     kvsh = None
     if world > 1 and not args.no_extra_legs:
@@ -478,6 +541,8 @@ def run_ours(args):
         line["kv_head_sharded"] = kvsh
     if gpu_ref is not None:
         line["gpu_reference"] = gpu_ref
+    if prefill is not None:
+        line["prefill_compress"] = prefill
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(w, steps=20, warmup=2)
     print(json.dumps(line), flush=True)

@@ -22,7 +22,7 @@ _DTYPES = {torch.float32: DKV_F32, torch.float16: DKV_F16, torch.bfloat16: DKV_B
 EXPORTS = (
     "dkv_version", "dkv_last_error", "dkv_fused_decode", "dkv_split_workspace_bytes", "dkv_split_decode",
     "dkv_split_combine", "dkv_two_stage_decode", "dkv_two_stage_decode_noalloc", "dkv_scores", "dkv_softmax_v", "dkv_append_decode",
-    "dkv_pack_bulk", "dkv_decompress", "dkv_gate_lengths", "dkv_gate_workspace_bytes",
+    "dkv_pack_bulk", "dkv_decompress", "dkv_gate_lengths", "dkv_gate_workspace_bytes", "dkv_project_bulk",
 )
 
 
@@ -74,6 +74,14 @@ class PackArgs(C.Structure):
     ]
 
 
+class ProjectArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32), ("n_tokens", C.c_int32), ("n_heads", C.c_int32),
+        ("x", C.c_void_p), ("x_stride", C.c_int64), ("basis", C.c_void_p), ("out", C.c_void_p), ("out_stride", C.c_int64),
+        ("status", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
 class GateArgs(C.Structure):
     _fields_ = [
         ("dtype", C.c_int32), ("n_rows", C.c_int32), ("dim", C.c_int32), ("low_rank", C.c_int32),
@@ -119,6 +127,8 @@ def load() -> C.CDLL:
     lib.dkv_gate_lengths.restype = C.c_int
     lib.dkv_gate_workspace_bytes.argtypes = [C.POINTER(GateArgs)]
     lib.dkv_gate_workspace_bytes.restype = C.c_size_t
+    lib.dkv_project_bulk.argtypes = [C.POINTER(ProjectArgs)]
+    lib.dkv_project_bulk.restype = C.c_int
     _lib = lib
     return lib
 

@@ -141,65 +141,144 @@ __global__ void __launch_bounds__(1024) append_project_kernel(dkv_append_args p,
   if (threadIdx.x == 0 && p.seq_lens && pos_ok) p.seq_lens[b] = pos + 1;
 }
 
-// One block per arena row: exclusive scan of the block's lengths, then row copies.
+// Bulk (prefill) pack.  One CTA per (block of 512 new tokens, arena row): every CTA sums the row's new lengths itself
+// (the part before its block gives its first offset, the whole gives the fits test -- a few KB from L2 against tens
+// of KB of payload), writes its tokens' metadata, and copies its payload with 16-byte copies when the layout allows
+// (16-bit elements, lengths multiples of 8, aligned bases and strides), element by element otherwise.  A row whose
+// block does not fit is flagged and left untouched by all of its CTAs.  The write pointers are read by every CTA, so
+// they are advanced by a second, one-thread-per-row kernel behind the copy.
+constexpr int PACK_THREADS = 512;
+
+template <int THREADS>
+__device__ __forceinline__ int2 block_sum2(int x, int y, int* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    x += __shfl_xor_sync(0xffffffffu, x, o);
+    y += __shfl_xor_sync(0xffffffffu, y, o);
+  }
+  __syncthreads();
+  if (lane == 0) { scratch[2 * warp] = x; scratch[2 * warp + 1] = y; }
+  __syncthreads();
+  int sx = 0, sy = 0;
+#pragma unroll
+  for (int w = 0; w < THREADS / 32; ++w) { sx += scratch[2 * w]; sy += scratch[2 * w + 1]; }
+  return make_int2(sx, sy);
+}
+
+struct pack_row {
+  int base, n_new, pos0;
+};
+__device__ __forceinline__ pack_row pack_row_of(const dkv_pack_args& p, int a, int b) {
+  pack_row r;
+  r.base = p.side.ptr[a];
+  r.n_new = p.row_counts ? min(max(p.row_counts[b], 0), p.n_new) : p.n_new;
+  r.pos0 = p.seq_lens ? p.seq_lens[b] : p.seq_pos;
+  return r;
+}
+__device__ __forceinline__ bool pack_fits(const dkv_pack_args& p, const pack_row& r, int total) {
+  return (int64_t)r.base + total <= p.side.flat_stride && r.pos0 >= 0 && r.pos0 + r.n_new <= p.seq_capacity;
+}
+
 template <typename T>
-__global__ void __launch_bounds__(256) pack_bulk_kernel(dkv_pack_args p) {
-  __shared__ int warp_tot[8];
-  __shared__ int carry_s;
-  const int a = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+__global__ void __launch_bounds__(PACK_THREADS) pack_bulk_kernel(dkv_pack_args p, int vec16) {
+  __shared__ int scratch[2 * PACK_THREADS / 32];
+  __shared__ int warp_tot[PACK_THREADS / 32];
+  const int a = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b = a / p.arenas_per_batch, j = a - b * p.arenas_per_batch;
   const dkv_side& sd = p.side;
-  const int base = sd.ptr[a];
-  const int n_new = p.row_counts ? min(max(p.row_counts[b], 0), p.n_new) : p.n_new;
-  const int pos0 = p.seq_lens ? p.seq_lens[b] : p.seq_pos;
-  if (tid == 0) carry_s = 0;
-  __syncthreads();
-
+  const pack_row r = pack_row_of(p, a, b);
+  const int s0 = blockIdx.x * PACK_THREADS;
+  if (s0 >= r.n_new && s0 > 0) return;
   const int32_t* nl = p.new_lens + (size_t)a * p.n_new;
-  for (int s0 = 0; s0 < n_new; s0 += 256) {
-    const int s = s0 + tid;
-    int len = 0;
-    if (s < n_new) len = checked_len(nl[s], p.max_dim, p.len_multiple, p.status, 0);
-    // block-wide exclusive scan
-    int incl = len;
+
+  // ---- the row's total (fits test) and the part before this block (first offset); bad lengths flagged once
+  int before = 0, rest = 0;
+  for (int s = tid; s < r.n_new; s += PACK_THREADS) {
+    const int len = checked_len(nl[s], p.max_dim, p.len_multiple, blockIdx.x == 0 ? p.status : nullptr, 0);
+    if (s < s0) before += len; else rest += len;
+  }
+  const int2 sums = block_sum2<PACK_THREADS>(before, rest, scratch);
+  if (!pack_fits(p, r, sums.x + sums.y)) {
+    if (tid == 0 && blockIdx.x == 0) set_status(p.status, DKV_ST_OVERFLOW);
+    return;  // metadata, payload and write pointer are left untouched
+  }
+
+  // ---- offsets of this block's tokens
+  const int s = s0 + tid;
+  const int len = s < r.n_new ? checked_len(nl[s], p.max_dim, p.len_multiple, nullptr, 1) : 0;
+  int incl = len;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    if (lane == 31) warp_tot[warp] = incl;
-    __syncthreads();
-    int wbase = 0;
-    for (int w = 0; w < warp; ++w) wbase += warp_tot[w];
-    const int carry = carry_s;
-    const int off = base + carry + wbase + incl - len;
-    if (s < n_new) {
-      const int pos = pos0 + s;
-      if (pos >= 0 && pos < p.seq_capacity) {
-        sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = len;
-        sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
-      }
-    }
-    __syncthreads();
-    if (tid == 255) carry_s = carry + wbase + incl;
-    __syncthreads();
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
   }
-  const int total = carry_s;
-  const bool fits = (int64_t)base + total <= sd.flat_stride && pos0 >= 0 && pos0 + n_new <= p.seq_capacity;
-  if (!fits) {
-    if (tid == 0) set_status(p.status, DKV_ST_OVERFLOW);
-    return;  // payload and write pointer are left untouched
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  int wbase = 0;
+  for (int w = 0; w < warp; ++w) wbase += warp_tot[w];
+  const int off = r.base + sums.x + wbase + incl - len;
+  if (s < r.n_new) {
+    const int pos = r.pos0 + s;
+    sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = len;
+    sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
   }
-  // payload: one warp per token row
+
+  // ---- payload of this warp's 32 tokens
   const T* st = reinterpret_cast<const T*>(p.states) + (size_t)b * p.stride_b + (size_t)j * p.stride_j;
   T* flat = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride;
-  for (int s = warp; s < n_new; s += 8) {
-    const int pos = pos0 + s;
-    const int len = sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s];
-    const int off = sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s];
-    copy_row(flat + off, st + (size_t)s * p.stride_s, len, lane);
+  const int half = lane >> 4, hl = lane & 15;
+  vec16 = vec16 && (r.base & 7) == 0;    // an arena written earlier with odd lengths falls back to element copies
+  if (vec16 && p.max_dim <= 128) {
+    // a row is at most 16 pieces of 16 bytes: one piece per lane of a half-warp, four pairs of rows in flight
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      uint4 v[4];
+      int roff[4];
+      bool on[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int li = i + 2 * u + half;
+        const int rlen = __shfl_sync(0xffffffffu, len, li);
+        roff[u] = __shfl_sync(0xffffffffu, off, li);
+        const int rs = s0 + 32 * warp + li;
+        on[u] = hl * 8 < rlen;      // rlen is 0 past the end of the block
+        if (on[u]) v[u] = __ldcs(reinterpret_cast<const uint4*>(st + (size_t)rs * p.stride_s) + hl);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (on[u]) reinterpret_cast<uint4*>(flat + roff[u])[hl] = v[u];
+    }
+  } else {
+    for (int i = 0; i < 32; i += 2) {
+      const int li = i + half;
+      const int rlen = __shfl_sync(0xffffffffu, len, li);
+      const int roff = __shfl_sync(0xffffffffu, off, li);
+      const int rs = s0 + 32 * warp + li;
+      if (rlen > 0) {
+        const T* src = st + (size_t)rs * p.stride_s;
+        T* dst = flat + roff;
+        if (vec16) {
+          for (int c = hl; c * 8 < rlen; c += 16)
+            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+        } else {
+          for (int e = hl; e < rlen; e += 16) dst[e] = src[e];
+        }
+      }
+    }
   }
-  if (tid == 0) sd.ptr[a] = base + total;
+}
+
+// Advances the write pointers behind pack_bulk_kernel: one CTA per arena row repeats the sum and the fits test.
+__global__ void __launch_bounds__(256) pack_advance_kernel(dkv_pack_args p) {
+  __shared__ int scratch[2 * 256 / 32];
+  const int a = blockIdx.x;
+  const pack_row r = pack_row_of(p, a, a / p.arenas_per_batch);
+  const int32_t* nl = p.new_lens + (size_t)a * p.n_new;
+  int total = 0;
+  for (int s = threadIdx.x; s < r.n_new; s += 256) total += checked_len(nl[s], p.max_dim, p.len_multiple, nullptr, 1);
+  const int2 sums = block_sum2<256>(total, 0, scratch);
+  if (threadIdx.x == 0 && pack_fits(p, r, sums.x)) p.side.ptr[a] = r.base + sums.x;
 }
 
 template <typename T>
@@ -271,9 +350,17 @@ extern "C" int dkv_pack_bulk(const dkv_pack_args* a) {
   if (int rc = check_side(a->side, "dkv_pack_bulk side")) return rc;
   const int n_arena = a->batch * a->arenas_per_batch;
   if (n_arena == 0 || a->n_new == 0) return DKV_OK;
+  DKV_REQUIRE(n_arena <= 65535, DKV_E_LIMIT, "dkv_pack_bulk: at most 65535 arena rows per call");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
-  if (a->dtype == DKV_F32) pack_bulk_kernel<float><<<n_arena, 256, 0, st>>>(*a);
-  else pack_bulk_kernel<uint16_t><<<n_arena, 256, 0, st>>>(*a);
+  // 16-byte copies when every row start is 16-byte aligned on both sides: 16-bit elements, lengths declared as
+  // multiples of 8 (offsets are then multiples of 8 too), aligned bases and strides
+  const bool two_byte = a->dtype != DKV_F32;
+  const int vec16 = two_byte && a->len_multiple % 8 == 0 && (((uintptr_t)a->states | (uintptr_t)a->side.flat) & 15) == 0 &&
+                    a->stride_b % 8 == 0 && a->stride_j % 8 == 0 && a->stride_s % 8 == 0 && a->side.flat_stride % 8 == 0;
+  const dim3 grid((unsigned)((a->n_new + PACK_THREADS - 1) / PACK_THREADS), (unsigned)n_arena);
+  if (a->dtype == DKV_F32) pack_bulk_kernel<float><<<grid, PACK_THREADS, 0, st>>>(*a, 0);
+  else pack_bulk_kernel<uint16_t><<<grid, PACK_THREADS, 0, st>>>(*a, vec16);
+  pack_advance_kernel<<<n_arena, 256, 0, st>>>(*a);
   DKV_CHECK_LAUNCH();
   return DKV_OK;
 }

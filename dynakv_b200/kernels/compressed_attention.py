@@ -28,6 +28,31 @@ def merge_basis(up: torch.Tensor, n_kv_heads: int, head_dim: int, low_rank: Opti
     return up[:, :rank].reshape(n_kv_heads, head_dim, rank).transpose(1, 2).contiguous()
 
 
+def project_bulk(x: torch.Tensor, basis: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Spectral coefficients of a block of pre-RoPE K (or V) rows for per-head bases, on the tensor core:
+    ``out[..., h*128 + r] = sum_d x[..., h*128 + d] * basis[h, r, d]``.  ``x`` [..., Hkv*128] (the projection layer's
+    output), ``basis`` [Hkv, 128, 128]; 16-bit types.  Stands in for the reference's one-time fold of the projection
+    into ``k_proj`` / ``v_proj`` (kernels/compressed_attention.py:267-275); the result is what ``update_sp`` takes."""
+    if not x.is_cuda:
+        raise RuntimeError("dynakv_b200 has no CPU path: project_bulk needs CUDA tensors")
+    n_heads = basis.shape[0]
+    if basis.shape[1:] != (128, 128) or x.shape[-1] != n_heads * 128 or basis.dtype != x.dtype:
+        raise ValueError("project_bulk takes x [..., Hkv*128] and basis [Hkv, 128, 128] of one 16-bit dtype")
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    o2 = out.view(-1, out.shape[-1])
+    a = _lib.ProjectArgs()
+    a.dtype, a.n_tokens, a.n_heads = _lib.dtype_code(x.dtype), x2.shape[0], n_heads
+    a.x, a.x_stride, a.basis = x2.data_ptr(), x2.stride(0), basis.contiguous().data_ptr()
+    a.out, a.out_stride = o2.data_ptr(), o2.stride(0)
+    a.status, a.stream = status_word(x.device).data_ptr(), _lib.stream_ptr(x.device)
+    _lib.check(_lib.load().dkv_project_bulk(C.byref(a)), "dkv_project_bulk")
+    return out
+
+
 _gate_scratch = {}
 
 
@@ -43,7 +68,7 @@ def _scratch(device, n_floats: int) -> torch.Tensor:
 
 def gate_lengths(states: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, low_rank: int,
                  threshold: float = 0.1, return_masked: bool = True, len_multiple: int = 1,
-                 native_rounding: bool = True):
+                 native_rounding: bool = True, out_lengths: Optional[torch.Tensor] = None):
     """Cutoff gate of one side (kernels/compressed_attention.py:84-119, one of the two halves of
     ``kv_process_fused``): ``states`` [..., d] spectral coefficient rows, ``weight`` [d, d], ``bias`` [d] or [1, d].
 
@@ -64,7 +89,12 @@ def gate_lengths(states: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
     if x.stride(-1) != 1:
         x = x.contiguous()
     w, b = weight.contiguous(), bias.reshape(-1).contiguous()
-    lengths = torch.empty(x.shape[0], dtype=torch.int32, device=states.device)
+    if out_lengths is not None:     # caller-owned output (e.g. a static buffer of a captured graph): nothing is allocated
+        if out_lengths.dtype != torch.int32 or out_lengths.numel() != x.shape[0] or not out_lengths.is_contiguous():
+            raise ValueError("out_lengths must be a contiguous int32 tensor with one entry per row")
+        lengths = out_lengths.view(-1)
+    else:
+        lengths = torch.empty(x.shape[0], dtype=torch.int32, device=states.device)
     masked = torch.empty((x.shape[0], d), dtype=states.dtype, device=states.device) if return_masked else None
     a = _lib.GateArgs()
     a.dtype, a.n_rows, a.dim, a.low_rank, a.threshold = _lib.dtype_code(states.dtype), x.shape[0], d, int(low_rank), threshold
@@ -96,7 +126,13 @@ class CompressedDecodeLayer:
 
     def __init__(self, layer_idx: int, k_up: torch.Tensor, v_up: torch.Tensor, theta: float,
                  policy: Optional[KernelPolicy] = None, k_norm_weight: Optional[torch.Tensor] = None,
-                 k_norm_eps: float = 1e-6, project_new_rows: bool = False):
+                 k_norm_eps: float = 1e-6, project_new_rows: bool = False, gate=None):
+        """``gate`` = (Wk, bk, Wv, bv) with [R, R] weights: the step then computes the cutoffs of the new coefficient
+        rows itself (kv_process_fused of the reference, one row per (sequence, KV head), lengths rounded up to the
+        cache's ``len_multiple``) before it appends them; ``new_k`` / ``new_v`` must then be coefficient rows."""
+        if gate is not None and project_new_rows:
+            raise ValueError("the gate takes coefficient rows: project the new rows before the step")
+        self.gate = gate
         self.layer_idx = layer_idx
         self.k_up, self.v_up = k_up.contiguous(), v_up.contiguous()
         self.theta = float(theta)
@@ -113,6 +149,11 @@ class CompressedDecodeLayer:
         new_k/new_v [B, Hkv, 128]: coefficient rows, or pre-RoPE head vectors when
         ``project_new_rows`` (they are then projected onto the basis inside the kernel).
         """
+        if self.gate is not None:
+            Wk, bk, Wv, bv = self.gate
+            R = new_k.shape[-1]
+            gate_lengths(new_k.view(-1, R), Wk, bk, R, return_masked=False, len_multiple=cache.len_multiple, out_lengths=len_k)
+            gate_lengths(new_v.view(-1, R), Wv, bv, R, return_masked=False, len_multiple=cache.len_multiple, out_lengths=len_v)
         ck, cv = cache.key_cache_sp[self.layer_idx], cache.value_cache_sp[self.layer_idx]
         a = _lib.AppendArgs()
         a.dtype = _lib.dtype_code(new_k.dtype)
@@ -178,7 +219,11 @@ class DecodeGraph:
         self._has_short = any(int(n) + 1 < switch for n in seq_lens_host)
         self._has_long = reach >= switch
         self._switch = switch
-        self.kernel_launches_per_step = L * (1 + (1 if self._has_short else 0) + (2 if self._has_long else 0))
+        self.kernel_launches_per_step = L * (1 + (1 if self._has_short else 0) + (2 if self._has_long else 0)) + \
+            4 * sum(1 for l in self.layers if l.gate is not None)
+        for l in self.layers:       # size the gate's scratch before any capture
+            if l.gate is not None:
+                _scratch(self.device, 8 * batch * Hkv * 128)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         status_word(self.device)
         self._run_layers(prepare_only=True)   # allocate the split workspace before any capture

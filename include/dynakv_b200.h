@@ -194,6 +194,26 @@ typedef struct dkv_pack_args {
  * Replaces the per-row python loop of _update_layer_cache (compressed_cache.py:184-209). */
 int dkv_pack_bulk(const dkv_pack_args* a);
 
+/* Bulk (prefill) projection of pre-RoPE rows onto per-head spectral bases on the tensor core:
+ *   out[t, h*128 + r] = sum_d x[t, h*128 + d] * basis[h, r, d]        (16-bit in and out, fp32 accumulation).
+ * Replaces the one-time fold of the projection into k_proj / v_proj
+ * (src/dynakv/kernels/compressed_attention.py:267-275): with per-head 128 x 128 bases the projection is applied to
+ * the projection layers' output instead, as a batched 128-wide GEMM over the tokens.  The result is what
+ * dkv_pack_bulk takes as `states`. */
+typedef struct dkv_project_args {
+  int32_t dtype;        /* DKV_F16 / DKV_BF16 */
+  int32_t n_tokens;     /* rows of x and out */
+  int32_t n_heads;      /* bases; a row holds n_heads * 128 elements */
+  const void* x;        /* [n_tokens, n_heads * 128], 16-byte aligned */
+  int64_t x_stride;     /* elements between rows, multiple of 8 */
+  const void* basis;    /* [n_heads, 128 (r), 128 (d)] contiguous */
+  void* out;            /* [n_tokens, n_heads * 128] */
+  int64_t out_stride;
+  int32_t* status;      /* optional device status word */
+  void* stream;
+} dkv_project_args;
+int dkv_project_bulk(const dkv_project_args* a);
+
 /* Ragged -> dense zero-padded [n_arena, n_tok, max_dim] (contiguous), gathered by offs.
  * Replaces simple_decompress (compressed_cache.py:36-56). */
 int dkv_decompress(int32_t dtype, int32_t n_arena, int32_t n_tok, int32_t max_dim, const dkv_side* side,

@@ -181,3 +181,78 @@ def test_ragged_batch_of_64_routes_on_the_device_across_the_switch_point():
     # the watched rows ended on both sides of the switch point and were served by different kernels on the way
     assert [policy.select(cur[b]) for b in (5, 17, 40)] == ["long_two_stage"] * 3
     assert policy.select(seq[5] + 1) == "short_fused"
+
+
+# ------------------------------------------------------------------ the cutoff gate replayed with the step
+def test_decode_graph_computes_the_cutoffs_with_the_gate():
+    """Coefficient rows in, the graph runs the gate (per (sequence, KV head) row, [128 x 128] weights, lengths rounded
+    up to multiples of 8), appends and attends; lengths against the oracle's gate in the same dtype, outputs against
+    the oracle's attention."""
+    seq = [620, 900]
+    cache, layers, cases, _ = _build(5217, seq, "beta:2,5", 500000.0, 1, project=False, extra=8)
+    gen = torch.Generator().manual_seed(77)
+    dt = torch.bfloat16
+    Wk = (torch.randn(128, 128, generator=gen) * 0.4).to(dt).to(DEV)
+    Wv = (torch.randn(128, 128, generator=gen) * 0.4).to(dt).to(DEV)
+    bk = (torch.randn(128, generator=gen) + torch.linspace(3.0, -3.0, 128)).to(dt).to(DEV)
+    bv = (torch.randn(128, generator=gen) + torch.linspace(3.0, -3.0, 128)).to(dt).to(DEV)
+    layers[0].gate = (Wk, bk, Wv, bv)
+    graph = DecodeGraph(layers, cache, 2, HQ, dt, DEV, seq)
+    graph.capture()
+    sigma = torch.exp(-torch.arange(128, dtype=torch.float32) / 24.0)
+    cur = list(seq)
+    for step in range(2):
+        q = torch.randn(1, 2, HQ, D, generator=gen).to(dt)
+        nk = (torch.randn(1, 2, HKV, D, generator=gen) * sigma).to(dt)
+        nv = (torch.randn(1, 2, HKV, D, generator=gen) * sigma).to(dt)
+        graph.q.copy_(q); graph.new_k.copy_(nk); graph.new_v.copy_(nv)
+        out = graph.step()[0]
+        torch.cuda.synchronize()
+        assert _common.read_status(torch.device(DEV)) == 0
+        for new, W, b, got in ((nk, Wk, bk, graph.len_k), (nv, Wv, bv, graph.len_v)):
+            want = O.gate_lengths(new.view(-1, 128), W.cpu(), b.cpu(), 128)         # the reference's ops in bf16
+            want8 = torch.clamp((want + 7) // 8 * 8, max=128)
+            diff = (got.view(-1).cpu().to(torch.int64) - want8.to(torch.int64)).abs()
+            assert int(diff.max()) <= 8 and int((diff != 0).sum()) <= 1      # at most one row moved by one position
+        cur = [n + 1 for n in cur]
+        st = cache.key_cache_sp[0]
+        assert torch.equal(st[1][:, cur[0] - 1].view(2, HKV)[0].cpu(), graph.len_k[0, 0].cpu())
+        ref = _oracle_rows(cache, 0, q[0], cases[0].k_up, cases[0].v_up, 500000.0, [0, 1], cur)
+        _check_rows(out, ref)
+
+
+# ------------------------------------------------------------------ bulk (prefill) compression at prompt length
+def test_bulk_projection_and_pack_at_prompt_length():
+    """An 8192-token prompt of 2 sequences: tensor-core projection onto the per-head bases against the oracle's fp32
+    projection (one rounding to bf16), then the bulk pack of the projected rows with Beta-distributed cutoffs,
+    bit-exact against the layout oracle."""
+    from dynakv_b200.kernels.compressed_attention import project_bulk
+    B, S = 2, 8192
+    gen = torch.Generator().manual_seed(61)
+    dt = torch.bfloat16
+    x = torch.randn(B, S, HKV * 128, generator=gen).to(dt)
+    basis = synthetic.qr_bases(HKV, 71, dt, "cpu")
+    coef = project_bulk(x.to(DEV), basis.to(DEV))
+    torch.cuda.synchronize()
+    assert _common.read_status(torch.device(DEV)) == 0
+    want = O.project_rows(x.view(B * S, HKV, 128).float(), basis.float()).reshape(B, S, HKV * 128)
+    err = (coef.float().cpu() - want).abs()
+    assert float(err.max()) <= 2.0 ** -8 * float(want.abs().max()) * 1.01
+    assert float(err.mean()) <= 2.0 ** -9 * float(want.abs().mean())
+    # a block that is not a whole tile, through a strided view
+    part = project_bulk(x[:1, :333].to(DEV), basis.to(DEV))
+    assert torch.equal(part.cpu(), coef[:1, :333].cpu())
+    # pack the projected rows
+    lens = synthetic.draw_lengths((B, HKV, S), "beta:2,5", gen)
+    cache = CustomDynamicCache(arenas_per_batch=HKV, len_multiple=8)
+    fk, fv, lk, lv, ok, ov = cache.update_sp(coef, lens.to(DEV), coef, lens.to(DEV), HKV * 128, 0, 128)
+    lay = O.LayoutOracle(B * HKV, np.float32)
+    rows = coef.float().cpu().view(B, S, HKV, 128).permute(0, 2, 1, 3).reshape(B * HKV, S, 128).numpy()
+    lay.update(rows, lens.view(B * HKV, S).numpy())
+    assert np.array_equal(lk.cpu().numpy(), lay.lens) and np.array_equal(ok.cpu().numpy(), lay.offs)
+    assert np.array_equal(cache.key_cache_sp[0][3].cpu().numpy(), lay.ptr)
+    f = fk.float().cpu().numpy()
+    for n in range(lay.n):
+        assert np.array_equal(f[n, : lay.ptr[n]], lay.flat[n])
+    assert torch.equal(fv[:, : int(lay.ptr.max())].cpu(), fk[:, : int(lay.ptr.max())].cpu())
+    assert _common.read_status(torch.device(DEV)) == 0

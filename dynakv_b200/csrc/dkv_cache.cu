@@ -141,30 +141,19 @@ __global__ void __launch_bounds__(1024) append_project_kernel(dkv_append_args p,
   if (threadIdx.x == 0 && p.seq_lens && pos_ok) p.seq_lens[b] = pos + 1;
 }
 
-// Bulk (prefill) pack.  One CTA per (block of 512 new tokens, arena row): every CTA sums the row's new lengths itself
-// (the part before its block gives its first offset, the whole gives the fits test -- a few KB from L2 against tens
-// of KB of payload), writes its tokens' metadata, and copies its payload with 16-byte copies when the layout allows
-// (16-bit elements, lengths multiples of 8, aligned bases and strides), element by element otherwise.  A row whose
-// block does not fit is flagged and left untouched by all of its CTAs.  The write pointers are read by every CTA, so
-// they are advanced by a second, one-thread-per-row kernel behind the copy.
-constexpr int PACK_THREADS = 512;
-
-template <int THREADS>
-__device__ __forceinline__ int2 block_sum2(int x, int y, int* scratch) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    x += __shfl_xor_sync(0xffffffffu, x, o);
-    y += __shfl_xor_sync(0xffffffffu, y, o);
-  }
-  __syncthreads();
-  if (lane == 0) { scratch[2 * warp] = x; scratch[2 * warp + 1] = y; }
-  __syncthreads();
-  int sx = 0, sy = 0;
-#pragma unroll
-  for (int w = 0; w < THREADS / 32; ++w) { sx += scratch[2 * w]; sy += scratch[2 * w + 1]; }
-  return make_int2(sx, sy);
-}
+// Bulk (prefill) pack, two kernels on the caller's stream.
+//  1. pack_scan_kernel, one CTA per (block of 1024 new tokens, arena row): validates the row's new lengths, adds
+//     them up (the whole for the fits test, the part before its block for its first offset) and writes lens / offs
+//     of its tokens.  A block whose payload does not fit is flagged and its tokens are recorded as empty (lens 0,
+//     offs = the write pointer: the rule of the decode append), so that attention never reads stale metadata for
+//     them; a block whose positions do not fit the metadata row is flagged and nothing is written.  The write
+//     pointer is read by every CTA of the row, so it is not advanced here.
+//  2. pack_copy_kernel, one CTA per (block of 256 new tokens, arena row): reads the metadata just written, copies
+//     the payload, and the CTA that holds the row's last new token advances the write pointer to that token's end.  A warp's 32 rows land back to back in the arena, so its payload is one run; with 16-bit elements,
+//     lengths multiples of 8 and aligned bases and strides the run moves as 16-byte pieces, one per lane whatever
+//     the rows' lengths (the source of a piece is found by a binary search over the rows' piece prefixes, held
+//     one per lane), four pieces per lane in flight; element by element otherwise.
+constexpr int SCAN_THREADS = 1024, COPY_THREADS = 256;
 
 struct pack_row {
   int base, n_new, pos0;
@@ -176,37 +165,66 @@ __device__ __forceinline__ pack_row pack_row_of(const dkv_pack_args& p, int a, i
   r.pos0 = p.seq_lens ? p.seq_lens[b] : p.seq_pos;
   return r;
 }
-__device__ __forceinline__ bool pack_fits(const dkv_pack_args& p, const pack_row& r, int total) {
-  return (int64_t)r.base + total <= p.side.flat_stride && r.pos0 >= 0 && r.pos0 + r.n_new <= p.seq_capacity;
+__device__ __forceinline__ bool positions_fit(const dkv_pack_args& p, const pack_row& r) {
+  return r.pos0 >= 0 && r.pos0 + r.n_new <= p.seq_capacity;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(PACK_THREADS) pack_bulk_kernel(dkv_pack_args p, int vec16) {
-  __shared__ int scratch[2 * PACK_THREADS / 32];
-  __shared__ int warp_tot[PACK_THREADS / 32];
+__global__ void __launch_bounds__(SCAN_THREADS) pack_scan_kernel(dkv_pack_args p) {
+  __shared__ int red[2 * SCAN_THREADS / 32];
+  __shared__ int warp_tot[SCAN_THREADS / 32];
   const int a = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int b = a / p.arenas_per_batch, j = a - b * p.arenas_per_batch;
   const dkv_side& sd = p.side;
-  const pack_row r = pack_row_of(p, a, b);
-  const int s0 = blockIdx.x * PACK_THREADS;
-  if (s0 >= r.n_new && s0 > 0) return;
+  const pack_row r = pack_row_of(p, a, a / p.arenas_per_batch);
+  const int s0 = blockIdx.x * SCAN_THREADS;
   const int32_t* nl = p.new_lens + (size_t)a * p.n_new;
-
-  // ---- the row's total (fits test) and the part before this block (first offset); bad lengths flagged once
+  if (s0 >= r.n_new && s0 > 0) return;
+  int32_t* flag = blockIdx.x == 0 ? p.status : nullptr;      // each fault is flagged by the row's first CTA
+  if (!positions_fit(p, r)) {
+    if (tid == 0) set_status(flag, DKV_ST_OVERFLOW);
+    return;
+  }
+  // ---- the row's total (fits test) and the part before this CTA's tokens (its first offset): every CTA of the row
+  // repeats the sum, four lengths per load, the repair path of checked_len only behind a cheap validity test
+  const int step = p.len_multiple, mask = (step & (step - 1)) == 0 ? step - 1 : -1;
+  auto valid_len = [&](int len) {
+    const bool bad = (unsigned)len > (unsigned)p.max_dim || (mask >= 0 ? (len & mask) : (len % step)) != 0;
+    return bad ? checked_len(len, p.max_dim, step, flag, 0) : len;
+  };
   int before = 0, rest = 0;
-  for (int s = tid; s < r.n_new; s += PACK_THREADS) {
-    const int len = checked_len(nl[s], p.max_dim, p.len_multiple, blockIdx.x == 0 ? p.status : nullptr, 0);
+  auto add = [&](int s, int len) {
+    len = valid_len(len);
     if (s < s0) before += len; else rest += len;
+  };
+  if ((reinterpret_cast<uintptr_t>(nl) & 15) == 0) {
+    const int n4 = r.n_new >> 2;
+    for (int q = tid; q < n4; q += SCAN_THREADS) {
+      const int4 v = __ldg(reinterpret_cast<const int4*>(nl) + q);
+      add(4 * q, v.x); add(4 * q + 1, v.y); add(4 * q + 2, v.z); add(4 * q + 3, v.w);
+    }
+    for (int s = 4 * n4 + tid; s < r.n_new; s += SCAN_THREADS) add(s, nl[s]);
+  } else {
+    for (int s = tid; s < r.n_new; s += SCAN_THREADS) add(s, nl[s]);
   }
-  const int2 sums = block_sum2<PACK_THREADS>(before, rest, scratch);
-  if (!pack_fits(p, r, sums.x + sums.y)) {
-    if (tid == 0 && blockIdx.x == 0) set_status(p.status, DKV_ST_OVERFLOW);
-    return;  // metadata, payload and write pointer are left untouched
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    before += __shfl_xor_sync(0xffffffffu, before, o);
+    rest += __shfl_xor_sync(0xffffffffu, rest, o);
   }
+  if (lane == 0) { red[2 * warp] = before; red[2 * warp + 1] = rest; }
+  __syncthreads();
+  before = red[2 * lane];
+  rest = red[2 * lane + 1];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    before += __shfl_xor_sync(0xffffffffu, before, o);
+    rest += __shfl_xor_sync(0xffffffffu, rest, o);
+  }
+  const bool fits = (int64_t)r.base + before + rest <= sd.flat_stride;
+  if (!fits && tid == 0) set_status(flag, DKV_ST_OVERFLOW);
 
-  // ---- offsets of this block's tokens
+  // ---- metadata of this CTA's 1024 tokens
   const int s = s0 + tid;
-  const int len = s < r.n_new ? checked_len(nl[s], p.max_dim, p.len_multiple, nullptr, 1) : 0;
+  const int len = (fits && s < r.n_new) ? valid_len(nl[s]) : 0;
   int incl = len;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -215,70 +233,82 @@ __global__ void __launch_bounds__(PACK_THREADS) pack_bulk_kernel(dkv_pack_args p
   }
   if (lane == 31) warp_tot[warp] = incl;
   __syncthreads();
-  int wbase = 0;
-  for (int w = 0; w < warp; ++w) wbase += warp_tot[w];
-  const int off = r.base + sums.x + wbase + incl - len;
+  int w_incl = warp_tot[lane];       // inclusive scan of the 32 warp totals, repeated by every warp
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, w_incl, o);
+    if (lane >= o) w_incl += t;
+  }
+  const int wbase = warp ? __shfl_sync(0xffffffffu, w_incl, warp - 1) : 0;
   if (s < r.n_new) {
     const int pos = r.pos0 + s;
     sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = len;
-    sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
-  }
-
-  // ---- payload of this warp's 32 tokens
-  const T* st = reinterpret_cast<const T*>(p.states) + (size_t)b * p.stride_b + (size_t)j * p.stride_j;
-  T* flat = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride;
-  const int half = lane >> 4, hl = lane & 15;
-  vec16 = vec16 && (r.base & 7) == 0;    // an arena written earlier with odd lengths falls back to element copies
-  if (vec16 && p.max_dim <= 128) {
-    // a row is at most 16 pieces of 16 bytes: one piece per lane of a half-warp, four pairs of rows in flight
-#pragma unroll
-    for (int i = 0; i < 32; i += 8) {
-      uint4 v[4];
-      int roff[4];
-      bool on[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int li = i + 2 * u + half;
-        const int rlen = __shfl_sync(0xffffffffu, len, li);
-        roff[u] = __shfl_sync(0xffffffffu, off, li);
-        const int rs = s0 + 32 * warp + li;
-        on[u] = hl * 8 < rlen;      // rlen is 0 past the end of the block
-        if (on[u]) v[u] = __ldcs(reinterpret_cast<const uint4*>(st + (size_t)rs * p.stride_s) + hl);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (on[u]) reinterpret_cast<uint4*>(flat + roff[u])[hl] = v[u];
-    }
-  } else {
-    for (int i = 0; i < 32; i += 2) {
-      const int li = i + half;
-      const int rlen = __shfl_sync(0xffffffffu, len, li);
-      const int roff = __shfl_sync(0xffffffffu, off, li);
-      const int rs = s0 + 32 * warp + li;
-      if (rlen > 0) {
-        const T* src = st + (size_t)rs * p.stride_s;
-        T* dst = flat + roff;
-        if (vec16) {
-          for (int c = hl; c * 8 < rlen; c += 16)
-            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
-        } else {
-          for (int e = hl; e < rlen; e += 16) dst[e] = src[e];
-        }
-      }
-    }
+    sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] =
+        r.base + (fits ? before : 0) + wbase + incl - len;
   }
 }
 
-// Advances the write pointers behind pack_bulk_kernel: one CTA per arena row repeats the sum and the fits test.
-__global__ void __launch_bounds__(256) pack_advance_kernel(dkv_pack_args p) {
-  __shared__ int scratch[2 * 256 / 32];
-  const int a = blockIdx.x;
-  const pack_row r = pack_row_of(p, a, a / p.arenas_per_batch);
-  const int32_t* nl = p.new_lens + (size_t)a * p.n_new;
-  int total = 0;
-  for (int s = threadIdx.x; s < r.n_new; s += 256) total += checked_len(nl[s], p.max_dim, p.len_multiple, nullptr, 1);
-  const int2 sums = block_sum2<256>(total, 0, scratch);
-  if (threadIdx.x == 0 && pack_fits(p, r, sums.x)) p.side.ptr[a] = r.base + sums.x;
+template <typename T>
+__global__ void __launch_bounds__(COPY_THREADS) pack_copy_kernel(dkv_pack_args p, int vec16) {
+  const int a = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b = a / p.arenas_per_batch, j = a - b * p.arenas_per_batch;
+  const dkv_side& sd = p.side;
+  const int n_new = p.row_counts ? min(max(p.row_counts[b], 0), p.n_new) : p.n_new;
+  const int pos0 = p.seq_lens ? p.seq_lens[b] : p.seq_pos;
+  const int s0 = blockIdx.x * COPY_THREADS + 32 * warp;      // this warp's first token
+  if (s0 >= n_new || pos0 < 0 || pos0 + n_new > p.seq_capacity) return;
+  const int s = s0 + lane;
+  int len = 0, off = 0;
+  if (s < n_new) {
+    const int pos = pos0 + s;
+    len = sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s];
+    off = sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s];
+    if (s == n_new - 1) sd.ptr[a] = off + len;
+  }
+  const int first_off = __shfl_sync(0xffffffffu, off, 0);
+  int run = off + len - first_off;                           // elements of the warp's run up to and with this row
+  run = __shfl_sync(0xffffffffu, run, min(31, n_new - 1 - s0));
+  if (run <= 0) return;
+  const T* rows = reinterpret_cast<const T*>(p.states) + (size_t)b * p.stride_b + (size_t)j * p.stride_j +
+                  (size_t)s0 * p.stride_s;
+  T* flat = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride + first_off;
+  const int pre = s < n_new ? off - first_off : run;         // elements of the run before this row
+  if (vec16 && (first_off & 7) == 0) {
+    const int n_pieces = run >> 3, pre8 = pre >> 3;
+    uint4* dst = reinterpret_cast<uint4*>(flat);
+    for (int g0 = 0; g0 < n_pieces; g0 += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int g = g0 + 32 * u + lane;
+        int i = 0;
+#pragma unroll
+        for (int bit = 16; bit > 0; bit >>= 1) {
+          const int cand = i + bit;                                        // <= 31 by construction
+          if (__shfl_sync(0xffffffffu, pre8, cand) <= g) i = cand;
+        }
+        const int first = __shfl_sync(0xffffffffu, pre8, i);
+        if (g < n_pieces) v[u] = __ldcs(reinterpret_cast<const uint4*>(rows + (size_t)i * p.stride_s) + (g - first));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int g = g0 + 32 * u + lane;
+        if (g < n_pieces) dst[g] = v[u];
+      }
+    }
+  } else {
+    for (int g0 = 0; g0 < run; g0 += 32) {
+      const int g = g0 + lane;
+      int i = 0;
+#pragma unroll
+      for (int bit = 16; bit > 0; bit >>= 1) {
+        const int cand = i + bit;
+        if (__shfl_sync(0xffffffffu, pre, cand) <= g) i = cand;
+      }
+      const int first = __shfl_sync(0xffffffffu, pre, i);
+      if (g < run) flat[g] = rows[(size_t)i * p.stride_s + (g - first)];
+    }
+  }
 }
 
 template <typename T>
@@ -357,10 +387,11 @@ extern "C" int dkv_pack_bulk(const dkv_pack_args* a) {
   const bool two_byte = a->dtype != DKV_F32;
   const int vec16 = two_byte && a->len_multiple % 8 == 0 && (((uintptr_t)a->states | (uintptr_t)a->side.flat) & 15) == 0 &&
                     a->stride_b % 8 == 0 && a->stride_j % 8 == 0 && a->stride_s % 8 == 0 && a->side.flat_stride % 8 == 0;
-  const dim3 grid((unsigned)((a->n_new + PACK_THREADS - 1) / PACK_THREADS), (unsigned)n_arena);
-  if (a->dtype == DKV_F32) pack_bulk_kernel<float><<<grid, PACK_THREADS, 0, st>>>(*a, 0);
-  else pack_bulk_kernel<uint16_t><<<grid, PACK_THREADS, 0, st>>>(*a, vec16);
-  pack_advance_kernel<<<n_arena, 256, 0, st>>>(*a);
+  const dim3 scan_grid((unsigned)((a->n_new + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)n_arena);
+  pack_scan_kernel<<<scan_grid, SCAN_THREADS, 0, st>>>(*a);
+  const dim3 grid((unsigned)((a->n_new + COPY_THREADS - 1) / COPY_THREADS), (unsigned)n_arena);
+  if (a->dtype == DKV_F32) pack_copy_kernel<float><<<grid, COPY_THREADS, 0, st>>>(*a, 0);
+  else pack_copy_kernel<uint16_t><<<grid, COPY_THREADS, 0, st>>>(*a, vec16);
   DKV_CHECK_LAUNCH();
   return DKV_OK;
 }

@@ -190,7 +190,10 @@ typedef struct dkv_pack_args {
 } dkv_pack_args;
 
 /* Bulk (prefill) pack of a block of tokens into one side: exclusive scan of the lengths, lens/offs
- * written, kept coefficients copied back to back, write pointer advanced.
+ * written, kept coefficients copied back to back, write pointer advanced (two kernels on `stream`).
+ * An arena row whose new payload would pass flat_stride sets DKV_ST_OVERFLOW, keeps its write pointer and records
+ * the block's tokens as empty (lens 0, offs = the write pointer: the rule of dkv_append_decode); a row whose
+ * positions would pass seq_capacity sets DKV_ST_OVERFLOW and is not touched at all.
  * Replaces the per-row python loop of _update_layer_cache (compressed_cache.py:184-209). */
 int dkv_pack_bulk(const dkv_pack_args* a);
 

@@ -219,6 +219,44 @@ def test_append_with_projection_and_status_flags():
     assert _common.read_status(torch.device(DEV)) & _lib.ST_OVERFLOW
 
 
+def test_bulk_pack_that_does_not_fit_records_empty_tokens_and_keeps_the_pointer():
+    """Row 0 of a 2-row cache has room for its block, row 1 does not: row 1 is flagged, keeps its write pointer and
+    its tokens are recorded as empty; a block past the sequence capacity is flagged and leaves the row untouched."""
+    import ctypes as C
+
+    from dynakv_b200 import _lib
+    dev = torch.device(DEV)
+    S, R = 40, 128
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(1, S, 2 * R, generator=gen).to(torch.bfloat16).to(dev)
+    lens = torch.full((1, 2, S), 8, dtype=torch.int32)
+    lens[0, 1] = 64
+    cache = CustomDynamicCache(arenas_per_batch=2, len_multiple=8)
+    cache.reserve(0, 1, 40 * 8 + 64, S + 8, torch.bfloat16, dev)      # 384 elements per arena row: 40*64 does not fit
+    ck = cache.key_cache_sp[0]
+    ck[1].fill_(-7)
+    p = _lib.PackArgs()
+    p.dtype, p.batch, p.arenas_per_batch, p.n_new, p.max_dim = _lib.DKV_BF16, 1, 2, S, R
+    p.states, p.stride_b, p.stride_j, p.stride_s = x.data_ptr(), x.stride(0), R, x.stride(1)
+    lens_d = lens.view(2, S).contiguous().to(dev)
+    p.new_lens, p.side = lens_d.data_ptr(), cache._side(ck)
+    p.seq_pos, p.seq_capacity, p.len_multiple = 0, ck[1].shape[1], 8
+    p.status, p.stream = _common.status_word(dev).data_ptr(), _lib.stream_ptr(dev)
+    _common.status_word(dev).zero_()
+    _lib.check(_lib.load().dkv_pack_bulk(C.byref(p)), "dkv_pack_bulk")
+    assert _common.read_status(dev) == _lib.ST_OVERFLOW
+    assert ck[3].tolist() == [S * 8, 0]
+    assert ck[1][0, :S].tolist() == [8] * S and ck[2][0, :S].tolist() == [8 * i for i in range(S)]
+    assert ck[1][1, :S].tolist() == [0] * S and ck[2][1, :S].tolist() == [0] * S
+    assert torch.equal(ck[0][0, : S * 8].view(S, 8), x[0, :, :8])
+    # positions past the metadata row: nothing is written
+    ck[1].fill_(-7)
+    p.seq_pos = ck[1].shape[1] - S + 1
+    _lib.check(_lib.load().dkv_pack_bulk(C.byref(p)), "dkv_pack_bulk")
+    assert _common.read_status(dev) & _lib.ST_OVERFLOW
+    assert bool((ck[1] == -7).all()) and ck[3].tolist() == [S * 8, 0]
+
+
 # ------------------------------------------------------------------ benchmark-shaped configurations
 def _case_args(case):
     fk, fv, lk, lv, ok, ov = case.views()

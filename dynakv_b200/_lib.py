@@ -60,6 +60,7 @@ class AppendArgs(C.Structure):
         ("k", Side), ("v", Side),
         ("seq_pos", C.c_int32), ("seq_lens", C.c_void_p), ("seq_capacity", C.c_int32),
         ("len_multiple", C.c_int32), ("status", C.c_void_p), ("stream", C.c_void_p),
+        ("tickets", C.c_void_p),
     ]
 
 

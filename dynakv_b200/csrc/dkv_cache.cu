@@ -141,6 +141,75 @@ __global__ void __launch_bounds__(1024) append_project_kernel(dkv_append_args p,
   if (threadIdx.x == 0 && p.seq_lens && pos_ok) p.seq_lens[b] = pos + 1;
 }
 
+// The same append with one CTA per (arena row, side): grid (2 * arenas_per_batch, batch), 8 warps that take 8 basis
+// rows each per iteration (at most two iterations).  Each CTA advances its own write pointer; the per-row token
+// counter is read by all CTAs of a batch row, so the last of them to finish (a ticket per batch row, left at zero
+// again) advances it.
+template <typename T>
+__global__ void __launch_bounds__(256) append_project_grid_kernel(dkv_append_args p) {
+  pdl_launch_dependents();
+  const int b = blockIdx.y, item = blockIdx.x, tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int A = p.arenas_per_batch;
+  const int pos = p.seq_lens ? p.seq_lens[b] : p.seq_pos;
+  const bool pos_ok = pos >= 0 && pos < p.seq_capacity;
+  if (!pos_ok && tid == 0 && item == 0) set_status(p.status, DKV_ST_OVERFLOW);
+  if (pos_ok) {
+    const int side_idx = item / A, j = item - side_idx * A;
+    const dkv_side& sd = side_idx ? p.v : p.k;
+    const int a = b * A + j;
+    const T* src = reinterpret_cast<const T*>(side_idx ? p.new_v : p.new_k) + (size_t)a * 128;
+    const int len = checked_len((side_idx ? p.len_v : p.len_k)[a], 128, p.len_multiple, p.status, tid);
+    const int off = sd.ptr[a];
+    const bool fits = (int64_t)off + len <= sd.flat_stride;
+    if (fits) {
+      T* dst = reinterpret_cast<T*>(sd.flat) + (size_t)a * sd.flat_stride + off;
+      const T* basis = reinterpret_cast<const T*>(side_idx ? p.v_basis : p.k_basis) + (size_t)j * 128 * 128;
+      float x[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = to_f32(src[lane * 4 + e]);
+      for (int r0 = warp * 8; r0 < len; r0 += 64) {
+        float acc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const T* row = basis + (size_t)(r0 + u) * 128 + lane * 4;   // r0 + u < 128 always (len <= 128, step 8)
+          float s = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s = fmaf(x[e], to_f32(row[e]), s);
+          acc[u] = s;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+        }
+        if (lane < 8 && r0 + lane < len) {
+          float v = acc[0];
+#pragma unroll
+          for (int u = 1; u < 8; ++u) v = (lane == u) ? acc[u] : v;
+          dst[r0 + lane] = from_f32<T>(v);
+        }
+      }
+    }
+    __syncthreads();   // every thread has read ptr[a]
+    if (tid == 0) {
+      if (!fits) set_status(p.status, DKV_ST_OVERFLOW);   // recorded as an empty token
+      sd.lens[(size_t)a * sd.lens_stride_a + (size_t)pos * sd.lens_stride_s] = fits ? len : 0;
+      sd.offs[(size_t)a * sd.offs_stride_a + (size_t)pos * sd.offs_stride_s] = off;
+      if (fits) sd.ptr[a] = off + len;
+    }
+  } else {
+    __syncthreads();
+  }
+  if (tid == 0 && p.seq_lens) {     // tid 0 read seq_lens[b] above; the barrier orders the other threads' reads
+    __threadfence();
+    if (atomicAdd(&p.tickets[b], 1) == 2 * A - 1) {
+      p.tickets[b] = 0;
+      if (pos_ok) p.seq_lens[b] = pos + 1;
+    }
+  }
+}
+
 // Bulk (prefill) pack, two kernels on the caller's stream.
 //  1. pack_scan_kernel, one CTA per (block of 1024 new tokens, arena row): validates the row's new lengths, adds
 //     them up (the whole for the fits test, the part before its block for its first offset) and writes lens / offs
@@ -357,9 +426,11 @@ extern "C" int dkv_append_decode(const dkv_append_args* a) {
   if (proj)
     DKV_REQUIRE(a->max_dim == 128 && a->dtype != DKV_F32 && items <= 32, DKV_E_ARG,
                 "dkv_append_decode: in-kernel projection needs 128-wide 16-bit rows and at most 16 arenas per batch row");
+  const bool per_item = proj && (a->seq_lens == nullptr || a->tickets != nullptr) && a->batch <= 65535;
 #define LAUNCH(T)                                                             \
   do {                                                                        \
-    if (proj) append_project_kernel<T><<<a->batch, 32 * wpi * items, 0, st>>>(*a, wpi); \
+    if (per_item) append_project_grid_kernel<T><<<dim3(items, a->batch), 256, 0, st>>>(*a); \
+    else if (proj) append_project_kernel<T><<<a->batch, 32 * wpi * items, 0, st>>>(*a, wpi); \
     else append_decode_kernel<T><<<a->batch, threads, 0, st>>>(*a);    \
   } while (0)
   if (a->dtype == DKV_F32) LAUNCH(float);

@@ -141,6 +141,12 @@ class CompressedDecodeLayer:
             k_norm_weight = k_norm_weight.to(device=k_up.device, dtype=torch.float32).contiguous()
         self.k_norm_weight, self.k_norm_eps = k_norm_weight, k_norm_eps
         self.project_new_rows = project_new_rows
+        self._tickets: Optional[torch.Tensor] = None
+
+    def prepare(self, batch: int, device) -> None:
+        """Allocate what ``append`` needs on the device (before any graph capture)."""
+        if self.project_new_rows and (self._tickets is None or self._tickets.numel() < batch):
+            self._tickets = torch.zeros(max(batch, 1), dtype=torch.int32, device=device)
 
     def append(self, cache: CustomDynamicCache, new_k, new_v, len_k, len_v, row_counter: torch.Tensor,
                seq_capacity: int) -> None:
@@ -160,7 +166,8 @@ class CompressedDecodeLayer:
         a.batch, a.arenas_per_batch, a.max_dim = new_k.shape[0], new_k.shape[1], new_k.shape[2]
         a.new_k, a.new_v, a.len_k, a.len_v = new_k.data_ptr(), new_v.data_ptr(), len_k.data_ptr(), len_v.data_ptr()
         if self.project_new_rows:
-            a.k_basis, a.v_basis = self.k_up.data_ptr(), self.v_up.data_ptr()
+            self.prepare(new_k.shape[0], new_k.device)
+            a.k_basis, a.v_basis, a.tickets = self.k_up.data_ptr(), self.v_up.data_ptr(), self._tickets.data_ptr()
         a.k, a.v = cache._side(ck), cache._side(cv)
         a.seq_pos, a.seq_lens, a.seq_capacity = 0, row_counter.data_ptr(), seq_capacity
         a.len_multiple = cache.len_multiple
@@ -221,7 +228,8 @@ class DecodeGraph:
         self._switch = switch
         self.kernel_launches_per_step = L * (1 + (1 if self._has_short else 0) + (2 if self._has_long else 0)) + \
             4 * sum(1 for l in self.layers if l.gate is not None)
-        for l in self.layers:       # size the gate's scratch before any capture
+        for l in self.layers:       # size the gate's scratch and the append's tickets before any capture
+            l.prepare(batch, self.device)
             if l.gate is not None:
                 _scratch(self.device, 8 * batch * Hkv * 128)
         self.graph: Optional[torch.cuda.CUDAGraph] = None

@@ -163,6 +163,10 @@ typedef struct dkv_append_args {
   int32_t len_multiple;     /* lengths must be multiples of this, else DKV_ST_BAD_LENGTH */
   int32_t* status;
   void* stream;
+  int32_t* tickets;         /* optional [batch], zero before the first call and left zero by every call: with it (or
+                               with seq_lens == NULL) the projecting append runs one CTA per (arena row, side)
+                               instead of one per batch row; the last CTA of a batch row advances seq_lens[b].
+                               Calls that share a tickets array must not overlap. */
 } dkv_append_args;
 
 /* Decode-step append of one token per arena row, K and V together, all rows in one launch.

@@ -920,20 +920,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
   if (*abort_flag && tid == 0) set_status(p.status, DKV_ST_TIMEOUT);
 }
 
-// Merge the split partials of one (batch row, query head) and project through Bv.
-// 128 threads; the partial records of the row are read with independent loads (weights first, then the
-// latent vectors 8 records at a time) so the kernel is not a chain of dependent L2 round trips.
-constexpr int COMBINE_MAX_PART = 160;   // >= CTAs per KV head (at most the SM count)
+// Merge the split partials of one (batch row, KV head) for its query heads and project through Bv.
+// 512 threads: thread (h, r) merges latent component r of head h over the row's partial records (online softmax
+// merge, eight records per round with independent loads); the 32 KB of Bv are fetched into registers before
+// anything else, so that their latency hides behind the merge, and are used for all heads of the group.
 template <typename T>
-__global__ void __launch_bounds__(128) split_combine_kernel(dkv_attn_args p) {
-  __shared__ float lat_s[128];
-  __shared__ float wgt_s[COMBINE_MAX_PART];
-  __shared__ float red_s[4][128];
+__global__ void __launch_bounds__(512) split_combine_kernel(dkv_attn_args p) {
+  __shared__ float lat_s[HP][128];
+  __shared__ float red_s[16][HP][128];
   const WsHeader* wh = reinterpret_cast<const WsHeader*>(p.workspace);
   const float* ws = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(p.workspace) + ws_header_bytes());
-  const int i = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int i = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = tid >> 7, r = tid & 127;
   if (row_routed_out(p, p.batch_index ? p.batch_index[i] : i)) return;   // the row belongs to the other kernel
-  const int G = p.n_q_heads / p.n_basis_groups, g = h / G, hl = h - g * G, R = p.rank;
+  const int G = p.n_q_heads / p.n_basis_groups, R = p.rank;
+  // Bv pieces of this thread: rows tid/16 + 32 j, columns 8 (tid % 16) .. +8
+  const int c8 = tid & 15, row0 = tid >> 4;
+  uint4 bv[4];
+  {
+    const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * D;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int row = row0 + 32 * j;
+      bv[j] = row < R ? __ldg(reinterpret_cast<const uint4*>(vup + (size_t)row * D) + c8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   const int n_cta = wh->n_cta, total_units = wh->total_units;
   const int u_lo = wh->prefix[i], u_hi = wh->prefix[i + 1];
   const size_t entries_per_group = (size_t)p.batch + n_cta;
@@ -945,79 +956,84 @@ __global__ void __launch_bounds__(128) split_combine_kernel(dkv_attn_args p) {
     while (k_lo > 0 && unit_begin(k_lo, n_cta, total_units) > u_lo) --k_lo;
     k_hi = min(n_cta - 1, (int)(((long long)u_hi * n_cta + total_units - 1) / total_units));
   }
-  const float* rec0 = ws + (((size_t)g * entries_per_group + (size_t)i) * HP + hl) * PART_STRIDE;
+  const float* rec0 = ws + (((size_t)g * entries_per_group + (size_t)i) * HP + h) * PART_STRIDE;
   const size_t rec_step = (size_t)HP * PART_STRIDE;   // record k sits at rec0 + k * rec_step
-  // pass 1: thread t looks at candidate CTA k_lo + t (the range never exceeds the block in practice; loop anyway)
-  float m_mine = -INFINITY, l_mine = 0.f;
-  float M = -INFINITY;
-  for (int base = k_lo; base <= k_hi; base += 128) {
-    const int k = base + tid;
-    float mk = -INFINITY;
-    if (k <= k_hi) {
-      const int ub = unit_begin(k, n_cta, total_units), ue = unit_begin(k + 1, n_cta, total_units);
-      if (ue > ub && ub < u_hi && ue > u_lo) { mk = rec0[k * rec_step]; l_mine = rec0[k * rec_step + 1]; m_mine = mk; }
-    }
-    M = fmaxf(M, mk);
-  }
-  M = warp_max(M);
-  if (lane == 0) red_s[0][warp] = M;
-  __syncthreads();
-  M = fmaxf(fmaxf(red_s[0][0], red_s[0][1]), fmaxf(red_s[0][2], red_s[0][3]));
-  __syncthreads();
-  // weights (k_hi - k_lo < 128 whenever the grid has at most 128 CTAs per head per row; larger ranges fall
-  // back to recomputing weights below)
-  const int span = k_hi - k_lo + 1;
-  const bool fits = span <= 128 && span <= COMBINE_MAX_PART;
-  float w_mine = (m_mine == -INFINITY) ? 0.f : exp2f(m_mine - M);
-  if (fits && tid < span) wgt_s[tid] = w_mine;
-  float L = warp_sum(w_mine * l_mine);
-  if (lane == 0) red_s[1][warp] = L;
-  __syncthreads();
-  L = red_s[1][0] + red_s[1][1] + red_s[1][2] + red_s[1][3];
-  // pass 2: latent vector, thread = latent index
-  float v = 0.f;
-  if (fits) {
-    int kk = 0;
-    for (; kk + 8 <= span; kk += 8) {
-      float x[8];
+  float M = -INFINITY, L = 0.f, v = 0.f;
+  if (h < G) {
+    for (int base = k_lo; base <= k_hi; base += 8) {
+      float m[8], l[8], x[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = wgt_s[kk + j] != 0.f ? rec0[(size_t)(k_lo + kk + j) * rec_step + 2 + tid] : 0.f;
+      for (int j = 0; j < 8; ++j) {
+        const int k = base + j;
+        m[j] = -INFINITY; l[j] = 0.f; x[j] = 0.f;
+        if (k <= k_hi) {
+          const int ub = unit_begin(k, n_cta, total_units), ue = unit_begin(k + 1, n_cta, total_units);
+          if (ue > ub && ub < u_hi && ue > u_lo) {
+            const float* rec = rec0 + (size_t)k * rec_step;
+            m[j] = __ldcg(rec); l[j] = __ldcg(rec + 1); x[j] = __ldcg(rec + 2 + r);
+          }
+        }
+      }
+      float cm = m[0];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v = fmaf(x[j], wgt_s[kk + j], v);
+      for (int j = 1; j < 8; ++j) cm = fmaxf(cm, m[j]);
+      const float newM = fmaxf(M, cm);
+      if (newM != -INFINITY) {
+        const float keep = exp2f(M - newM);     // 0 while nothing was merged yet
+        L *= keep; v *= keep;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float w = m[j] == -INFINITY ? 0.f : exp2f(m[j] - newM);
+          L = fmaf(w, l[j], L);
+          v = fmaf(w, x[j], v);
+        }
+        M = newM;
+      }
     }
-    for (; kk < span; ++kk)
-      if (wgt_s[kk] != 0.f) v = fmaf(rec0[(size_t)(k_lo + kk) * rec_step + 2 + tid], wgt_s[kk], v);
-  } else {
-    L = 0.f;
-    for (int k = k_lo; k <= k_hi; ++k) {
-      const int ub = unit_begin(k, n_cta, total_units), ue = unit_begin(k + 1, n_cta, total_units);
-      if (!(ue > ub && ub < u_hi && ue > u_lo)) continue;
-      const float mw = rec0[k * rec_step];
-      const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      v = fmaf(rec0[k * rec_step + 2 + tid], wgt, v);
-      L = fmaf(rec0[k * rec_step + 1], wgt, L);
+    if (L <= 0.f && r == 0) set_status(p.status, DKV_ST_EMPTY_ROW);
+  }
+  lat_s[h][r] = L > 0.f ? v / L : 0.f;
+  __syncthreads();
+  // projection: out[hh][8 c8 + e] += lat[hh][row] * Bv[row][8 c8 + e] over this thread's four rows
+  float acc[HP][8];
+#pragma unroll
+  for (int hh = 0; hh < HP; ++hh)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[hh][e] = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int row = row0 + 32 * j;
+    const T* bp = reinterpret_cast<const T*>(&bv[j]);
+    float b[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) b[e] = to_f32(bp[e]);
+#pragma unroll
+    for (int hh = 0; hh < HP; ++hh) {
+      const float lr = lat_s[hh][row];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[hh][e] = fmaf(lr, b[e], acc[hh][e]);
     }
   }
-  lat_s[tid] = L > 0.f ? v / L : 0.f;
-  if (L <= 0.f && tid == 0) set_status(p.status, DKV_ST_EMPTY_ROW);
-  __syncthreads();
-  // projection: warp w takes latent rows w, w+4, ...; lane covers 4 output dims; partial sums merged in smem
-  const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * D;
-  float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll 4
-  for (int r = warp; r < R; r += 4) {
-    const float lr = lat_s[r];
-    const T* row = vup + (size_t)r * D + lane * 4;
-    o0 = fmaf(lr, to_f32(row[0]), o0); o1 = fmaf(lr, to_f32(row[1]), o1);
-    o2 = fmaf(lr, to_f32(row[2]), o2); o3 = fmaf(lr, to_f32(row[3]), o3);
+#pragma unroll
+  for (int hh = 0; hh < HP; ++hh)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[hh][e] += __shfl_xor_sync(0xffffffffu, acc[hh][e], 16);
+  if (lane < 16) {
+#pragma unroll
+    for (int hh = 0; hh < HP; ++hh) {
+      *reinterpret_cast<float4*>(&red_s[warp][hh][8 * c8]) = make_float4(acc[hh][0], acc[hh][1], acc[hh][2], acc[hh][3]);
+      *reinterpret_cast<float4*>(&red_s[warp][hh][8 * c8 + 4]) = make_float4(acc[hh][4], acc[hh][5], acc[hh][6], acc[hh][7]);
+    }
   }
-  red_s[warp][lane * 4 + 0] = o0; red_s[warp][lane * 4 + 1] = o1;
-  red_s[warp][lane * 4 + 2] = o2; red_s[warp][lane * 4 + 3] = o3;
   __syncthreads();
-  const float o = red_s[0][tid] + red_s[1][tid] + red_s[2][tid] + red_s[3][tid];
-  const int b = p.batch_index ? p.batch_index[i] : i;
-  T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)h * p.out_stride_h;
-  op[tid] = from_f32<T>(o);
+  if (h < G) {
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < 16; ++w) o += red_s[w][h][r];
+    const int b = p.batch_index ? p.batch_index[i] : i;
+    T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)(g * G + h) * p.out_stride_h;
+    op[r] = from_f32<T>(o);
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -1087,11 +1103,11 @@ int mma_combine(const dkv_attn_args* a) {
   if (a->batch == 0) return DKV_OK;
   DKV_REQUIRE(a->workspace != nullptr, DKV_E_WORKSPACE, "combine needs the split workspace");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
-  dim3 grid(a->batch, a->n_q_heads);
+  dim3 grid(a->batch, a->n_basis_groups);
   // launched the ordinary way: measured, an early (programmatic) launch of the combine or of the next append
   // costs more than it hides -- their CTAs wait on the SMs the decode kernel is using
-  if (a->dtype == DKV_BF16) split_combine_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(*a);
-  else split_combine_kernel<__half><<<grid, 128, 0, st>>>(*a);
+  if (a->dtype == DKV_BF16) split_combine_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(*a);
+  else split_combine_kernel<__half><<<grid, 512, 0, st>>>(*a);
   DKV_CHECK_LAUNCH();
   return DKV_OK;
 }

@@ -49,7 +49,8 @@ constexpr int W_MMA = 10;              // tcgen05.mma issuer for products (1), (
 constexpr int W_ROT = 14;              // query rotator
 constexpr int W_MMA2 = 11;             // tcgen05.mma issuer for product (3)
 constexpr int W_G2 = 16;               // gather warps 16, 17 (K) and 18, 19 (V): the second half of each side's four
-constexpr int NTHREADS = 20 * 32;      // at most 102 registers per thread
+constexpr int W_ROPE2 = 20;            // RoPE warps 20-23: the second half of each token's pairs (sub-partition w % 4 again)
+constexpr int NTHREADS = 24 * 32;      // at most 85 registers per thread
 constexpr int ST_TOK = 128;            // tokens per tile = rows of one UMMA
 constexpr int NBUF_A = 3;              // K operand tiles in shared memory (on the critical ring: three in flight)
 constexpr int NBUF_T = 3;              // K accumulator buffers in tensor memory (held from product (1) to product (2))
@@ -60,7 +61,7 @@ constexpr int MSLOT = PD + 1;          // metadata staging slots (private to the
 constexpr int KV_RING = 8;             // tiles of token-validity masks kept
 // 1/rms ring: a RoPE write for tile c only implies that the softmax warps have finished tile c-5 (product (1) of c
 // needs product (2) of c-3 issued, which needs the P tile of c-5), so tiles c-4 .. c may be unread
-constexpr int RS_RING = 8;
+constexpr int RS_RING = 5;
 static_assert(RS_RING >= 5, "1/rms ring must cover the RoPE warps' lead over the softmax warps");
 constexpr int TILE_BYTES = ST_TOK * 128 * 2;   // 128 tokens x 128 coefficients, chunk-major
 constexpr int Q_LBO = 272;             // byte distance of the 8-dim chunks of the rotated-query tile (bank spread)
@@ -84,7 +85,7 @@ struct SmemLayout {
   alignas(16) float lat[HP][128];                           // fused path: normalised latent result of a row
   alignas(16) float tmax[2][4][4];                          // [tile parity][warp][head]
   alignas(16) float lsum[4][4];                             // [warp][head]
-  alignas(16) float rs_buf[RS_RING][ST_TOK];                // K-RMSNorm: 1/rms of the tokens of the last tiles
+  alignas(16) float rs_buf[RS_RING][2][ST_TOK];             // K-RMSNorm: sum of squares of each half of the tokens' K rows, last tiles
   alignas(16) float knorm_w[D];
   uint32_t kvalid[KV_RING][4];                              // bit l of word w: token 32w + l of the tile has a K row
   alignas(8) unsigned long long a_full[NBUF_A];    // K operand tile written (128 gather lanes)
@@ -92,7 +93,7 @@ struct SmemLayout {
   alignas(8) unsigned long long v_free[NBUF_V];    // product (3) done with it (commit)
   alignas(8) unsigned long long q_full[NQ];        // rotated queries written (rotator)
   alignas(8) unsigned long long t_ready[NBUF_T];   // K accumulator written (commit)
-  alignas(8) unsigned long long kp_ready[NBUF_T];  // K' written back to tensor memory (4 RoPE warps)
+  alignas(8) unsigned long long kp_ready[NBUF_T];  // K' written back to tensor memory (8 RoPE warps)
   alignas(8) unsigned long long s_ready[NGROUP];   // scores written (commit)
   alignas(8) unsigned long long p_ready[NGROUP];   // P tile written (4 token warps)
   alignas(8) unsigned long long pv_done[NGROUP];   // product (3) done: O updated, P tile free (commit)
@@ -328,7 +329,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       mbar_init(smem_u32(&sm.p_ready[s]), 4);
       mbar_init(smem_u32(&sm.pv_done[s]), 1);
     }
-    for (int s = 0; s < NBUF_T; ++s) { mbar_init(smem_u32(&sm.t_ready[s]), 1); mbar_init(smem_u32(&sm.kp_ready[s]), 4); }
+    for (int s = 0; s < NBUF_T; ++s) { mbar_init(smem_u32(&sm.t_ready[s]), 1); mbar_init(smem_u32(&sm.kp_ready[s]), 8); }
     mbar_init(smem_u32(&sm.grp_sync), 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -518,7 +519,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
   }
 
-  else if (warp == W_KG0 || warp == W_KG0 + 4 || warp == W_VG0 || warp == W_VG0 + 4 || warp >= W_G2) {
+  else if (warp == W_KG0 || warp == W_KG0 + 4 || warp == W_VG0 || warp == W_VG0 + 4 || (warp >= W_G2 && warp < W_ROPE2)) {
     // =========================== gather warps ===========================
     // Four warps per side; lane l of gather warp j owns token 32j + l of every tile: it stages the token's length
     // and offset (cp.async, PD tiles ahead, slots private to the lane) and copies the coefficient row into the
@@ -638,9 +639,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           const uint32_t kp = tmem_base + TM_K + qt * 128;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            // A: K' of the tile, dims 16ks..16ks+15 = packed columns 8ks.. (dims < 64) or 64 + 8(ks-4).. (dims >= 64)
+            // A: K' of the tile, dims 16ks..16ks+15 = 8 packed columns; each 32-dim quarter of the row starts its
+            // 16 packed columns at the quarter's own first column (0, 32, 64, 96)
             // B: K-major, head rows 16 B apart inside a core matrix, 8-row groups 128 B (SBO), dim chunks Q_LBO apart
-            umma_f16_ta(tmem_base + TM_S + 16 * qg, kp + (ks < 4 ? 8 * ks : 64 + 8 * (ks - 4)),
+            umma_f16_ta(tmem_base + TM_S + 16 * qg, kp + 32 * (ks >> 1) + 8 * (ks & 1),
                         umma_desc(q_addr + ks * 2 * Q_LBO, Q_LBO, 128), idesc_s, ks > 0 ? 1u : 0u);
           }
           umma_commit(smem_u32(&sm.s_ready[qg]));   // also frees the rotated queries (the rotator waits on it too)
@@ -696,13 +698,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     }
   }
 
-  else if (warp < 4) {
+  else if (warp < 4 || warp >= W_ROPE2) {
     // ============================= RoPE warps =============================
-    // Thread (warp, lane) owns token 32 warp + lane of every tile, which is tensor-memory lane 32 warp + lane --
-    // the lanes a warp in SM sub-partition `warp` may access.  It turns the K row of product (1) into K' for
-    // product (2); it knows nothing about batch rows.
-    const int tok = tid;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * warp) << 16);
+    // Two threads per token: threads (w, lane) and (W_ROPE2 + w, lane) own token 32 w + lane of every tile, which is
+    // tensor-memory lane 32 w + lane -- the lanes a warp in SM sub-partition w may access.  The first takes the
+    // rotation pairs j = 0..31 (dims j and 64 + j), the second j = 32..63.  They turn the K row of product (1) into
+    // K' for product (2) in place: each 32-dim quarter of the row is packed into the first 16 columns of the
+    // quarter, columns its own thread has read before, so the two threads never touch each other's columns.
+    // They know nothing about batch rows.
+    const int w4 = warp & 3, half = warp >= W_ROPE2 ? 1 : 0;
+    const int tok = 32 * w4 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * w4) << 16);
     int buf = 0;            // accumulator buffer c % 3 and its phase (c / 3) & 1
     uint32_t bpar = 0;
     for (int c = 0; c < n_stages; ++c) {
@@ -712,9 +718,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       // ---------------- K row from tensor memory: [RMSNorm,] RoPE, K' back as packed 16-bit pairs ----------------
       float ss = 0.f;
 #pragma unroll 1   // kept rolled: the warp roles of an SM sub-partition share a small instruction cache
-      for (int i = 0; i < 8; ++i) {
+      for (int ii = 0; ii < 4; ++ii) {
         // pairs j = 8i..8i+7: dims j (columns 8i..) and j+64 (columns 64+8i..); table cells 8i..: per two pairs
         // one word {cos_j, cos_j+1} and one word {sin_j, sin_j+1} in fp16
+        const int i = 4 * half + ii;
         float lo[8], hi[8];
         uint32_t tg[8];
         tmem_ld_rope_chunk(lo, hi, tg, k_addr + 8 * i, k_addr + 64 + 8 * i, lane_addr + TM_TRIG + 8 * i);
@@ -745,11 +752,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
           plo[m] = Pack<T>::two(lo2.x, lo2.y);
           phi[m] = Pack<T>::two(hi2.x, hi2.y);
         }
-        // packed columns 4i.. (dims 8i..8i+7) and 64+4i.. (dims 64+8i..): both lie inside columns already read
-        tmem_st4(k_addr + 4 * i, plo[0], plo[1], plo[2], plo[3]);
-        tmem_st4(k_addr + 64 + 4 * i, phi[0], phi[1], phi[2], phi[3]);
+        // dims 8i..8i+7 -> packed columns 32 half + 4 ii.., dims 64+8i.. -> 64 + 32 half + 4 ii..: inside the
+        // columns this thread read in this or an earlier round
+        tmem_st4(k_addr + 32 * half + 4 * ii, plo[0], plo[1], plo[2], plo[3]);
+        tmem_st4(k_addr + 64 + 32 * half + 4 * ii, phi[0], phi[1], phi[2], phi[3]);
       }
-      if (KNORM) sm.rs_buf[c % RS_RING][tok] = rsqrtf(ss * (1.0f / D) + p.k_norm_eps);
+      if (KNORM) sm.rs_buf[c % RS_RING][half][tok] = ss;
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -789,7 +797,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       float s[HP];
       tmem_ld4(s, lane_addr + TM_S + 16 * buf);
       if (KNORM) {
-        const float rs = sm.rs_buf[c % RS_RING][tok];
+        const float rs = rsqrtf((sm.rs_buf[c % RS_RING][0][tok] + sm.rs_buf[c % RS_RING][1][tok]) * (1.0f / D) + p.k_norm_eps);
 #pragma unroll
         for (int h = 0; h < HP; ++h) s[h] *= rs;
       }

@@ -629,7 +629,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-reference", action="store_true", help="skip the reference's Triton kernels at N=1")
     ap.add_argument("--no-extra-legs", action="store_true", help="skip the ragged strong-scaling and KV-head-sharded legs")
+    ap.add_argument("--prefill-only", type=int, default=0, metavar="REPS",
+                    help="only time the bulk (prefill) projection and pack with REPS launches each, print that object")
     args = ap.parse_args()
+    if args.prefill_only > 0:
+        torch.cuda.set_device(0)
+        print(json.dumps(prefill_compress_leg(torch.device("cuda:0"), args.prefill_only)))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

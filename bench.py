@@ -348,6 +348,25 @@ def prefill_compress_leg(dev, reps=200):
                           "of_hbm_peak": 2 * payload / (ms_pack * 1e-3) / 1e9 / hbm, "retention": payload / (x.numel() * 2)}}
 
 
+def tensor_pipe_probe(dev, tiles=100):
+    """Cycles per 128-token tile that one SM's tensor pipe is held by the decode kernel's three tcgen05.mma chains
+    (issued back to back by one thread, nothing else on the SM): the floor under the split kernel's time per tile."""
+    from dynakv_b200 import _lib
+    from dynakv_b200.kernels._common import status_word, read_status
+    lib = _lib.load()
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    cyc = torch.zeros(n_sm, dtype=torch.int64, device=dev)
+    out = {}
+    for name, mask in (("k_reconstruction", 1), ("scores", 2), ("latent_accumulation", 4), ("all_three", 7)):
+        for _ in range(2):
+            _lib.check(lib.dkv_probe_tensor_pipe(mask, tiles, n_sm, cyc.data_ptr(), status_word(dev).data_ptr(),
+                                                 _lib.stream_ptr(dev)), "dkv_probe_tensor_pipe")
+        torch.cuda.synchronize()
+        out[name] = float(cyc.double().median().item()) / tiles
+    out["status"] = read_status(dev)
+    return {"cycles_per_tile": out, "tiles": tiles, "ctas": n_sm}
+
+
 def gpu_reference_leg(graph, cache, w, dev):
     """The reference's own Triton kernels (abx_sparse -> avx, and the fused kernel) on layer 0 of the workload, one call
     pair per KV head (the reference API with a single basis group is the per-head layout), CUDA-event timed."""
@@ -631,10 +650,16 @@ def main():
     ap.add_argument("--no-extra-legs", action="store_true", help="skip the ragged strong-scaling and KV-head-sharded legs")
     ap.add_argument("--prefill-only", type=int, default=0, metavar="REPS",
                     help="only time the bulk (prefill) projection and pack with REPS launches each, print that object")
+    ap.add_argument("--pipe-probe", action="store_true",
+                    help="only run the tensor-pipe occupancy probe of the decode kernel's products, print that object")
     args = ap.parse_args()
     if args.prefill_only > 0:
         torch.cuda.set_device(0)
         print(json.dumps(prefill_compress_leg(torch.device("cuda:0"), args.prefill_only)))
+        return
+    if args.pipe_probe:
+        torch.cuda.set_device(0)
+        print(json.dumps(tensor_pipe_probe(torch.device("cuda:0"))))
         return
     if args.impl == "reference":
         run_reference(args)

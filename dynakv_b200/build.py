@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdynakv_b200.so")
-SOURCES = ["dkv_api.cu", "dkv_cache.cu", "dkv_generic.cu", "dkv_gate.cu", "dkv_mma_decode.cu", "dkv_project.cu"]
+SOURCES = ["dkv_api.cu", "dkv_cache.cu", "dkv_generic.cu", "dkv_gate.cu", "dkv_mma_decode.cu", "dkv_project.cu", "dkv_pipe_probe.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "-cudart", "shared",

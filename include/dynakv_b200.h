@@ -201,6 +201,14 @@ typedef struct dkv_pack_args {
  * Replaces the per-row python loop of _update_layer_cache (compressed_cache.py:184-209). */
 int dkv_pack_bulk(const dkv_pack_args* a);
 
+/* Diagnostic, no counterpart in the reference: clock cycles per 128-token tile that the tensor pipe of one SM is
+ * held by the decode kernel's tcgen05.mma chains, issued back to back by one thread over zero operands with nothing
+ * else running on the SM.  `products` is a mask: 1 = K reconstruction (8 x M128 N128 K16), 2 = scores (8 x M128 N16
+ * K16, A in tensor memory), 4 = latent accumulation (8 x M128 N16 K16).  Launches n_cta CTAs (one per SM when
+ * n_cta <= the SM count) of `tiles` tiles each and writes cycles[c] = elapsed clock64 of CTA c for all its tiles.
+ * The wait for the products is bounded; DKV_ST_TIMEOUT is set in *status when it runs out. */
+int dkv_probe_tensor_pipe(int32_t products, int32_t tiles, int32_t n_cta, int64_t* cycles, int32_t* status, void* stream);
+
 /* Bulk (prefill) projection of pre-RoPE rows onto per-head spectral bases on the tensor core:
  *   out[t, h*128 + r] = sum_d x[t, h*128 + d] * basis[h, r, d]        (16-bit in and out, fp32 accumulation).
  * Replaces the one-time fold of the projection into k_proj / v_proj

@@ -230,7 +230,9 @@ class MiniLlama:
     @torch.no_grad()
     def decode_step(self, ids: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
         """Append the token ``ids`` [B] to every row and return the next greedy token [B] (and keep the logits in
-        ``self.logits``).  With ``use_graph`` (single rank) the step is captured once and replayed."""
+        ``self.logits``).  With ``use_graph`` (single-rank models only) the step is captured once and replayed.  A
+        tensor-parallel rank always runs the step eagerly: a captured step with ``torch.distributed`` all-reduces
+        inside did not finish on two GPUs, and is not offered."""
         if use_graph and self.tp_size == 1 and self.trace is None:
             if self._graph is None:
                 self._ids = ids.clone()

@@ -57,3 +57,43 @@ def test_generated_tokens_attend_like_the_oracle_and_the_graph_replays_the_eager
         assert torch.allclose(replay.logits.float().cpu(), logits[step], atol=2e-3, rtol=0), step
     assert replay.cache.seq_lens(1).tolist() == [P + NEW] * 3
     assert _common.read_status(torch.device(DEV)) == 0
+
+
+def _tp_worker(rank, world, port, ids, new_tokens, out_path):
+    import os
+
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    model = MiniLlama(TINY, dev, seed=5, tp_rank=rank, tp_size=world)
+    nxt = model.prefill(ids.to(dev), new_tokens + 4)
+    logits = []
+    for _ in range(new_tokens):
+        nxt = model.decode_step(nxt.clone())
+        logits.append(model.logits.float().cpu())
+    if rank == 0:
+        torch.save(torch.stack(logits), out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_sharded_by_kv_head_give_the_logits_of_one_rank(tmp_path):
+    """Tensor parallel by KV head on 2 GPUs (this package's kernels on each rank's heads, NCCL all-reduce after the
+    row-parallel output and down projections) against the same model on one GPU."""
+    import torch.multiprocessing as mp
+    P, NEW = 520, 3
+    gen = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, TINY.vocab, (2, P), generator=gen)
+    out_path = str(tmp_path / "tp_logits.pt")
+    mp.spawn(_tp_worker, args=(2, 29533, ids, NEW, out_path), nprocs=2, join=True)
+    got = torch.load(out_path)
+    model = MiniLlama(TINY, DEV, seed=5)
+    nxt = model.prefill(ids.to(DEV), NEW + 4)
+    for step in range(NEW):
+        nxt = model.decode_step(nxt.clone())
+        want = model.logits.float().cpu()
+        # bf16 partial sums are added in a different order: a few units of bf16 rounding on logits of size ~0.3
+        assert float((got[step] - want).abs().max()) <= 2e-2 * float(want.abs().max()) + 1e-3, step

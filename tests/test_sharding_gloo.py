@@ -79,3 +79,40 @@ def test_block_ranges_cover_everything_once():
     with pytest.raises(ValueError):
         sharding.shard_kv_heads(8, 32, 3, 0)
     assert sharding.shard_kv_heads(8, 32, 4, 1) == ((2, 4), (8, 16))
+
+
+def _runner_worker(rank, port, results):
+    """The decode runner's tensor-parallel shards on CPU: the column shards of the projections put side by side are
+    the one-rank matrices, and the row-parallel output / MLP paths with their all-reduce give the one-rank result.
+    (The attention itself needs the CUDA kernels and is covered by the two-GPU test.)"""
+    from dynakv_b200.runner import MiniLlama, ModelShape, rms_norm
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        shape = ModelShape(layers=1, hidden=256, mlp=512, vocab=64, n_q_heads=8, n_kv_heads=4)
+        one = MiniLlama(shape, "cpu", dtype=torch.float32, seed=9)
+        mine = MiniLlama(shape, "cpu", dtype=torch.float32, seed=9, tp_rank=rank, tp_size=WORLD)
+        w1, wr = one.layers[0], mine.layers[0]
+        (k_lo, k_hi), (q_lo, q_hi) = sharding.shard_kv_heads(shape.n_kv_heads, shape.n_q_heads, WORLD, rank)
+        cols_ok = (torch.equal(wr.wq, w1.wq[:, q_lo * 128:q_hi * 128]) and torch.equal(wr.wk, w1.wk[:, k_lo * 128:k_hi * 128])
+                   and torch.equal(wr.k_up, w1.k_up[k_lo:k_hi]) and torch.equal(wr.v_up, w1.v_up[k_lo:k_hi])
+                   and torch.equal(wr.w_cut, torch.cat((w1.w_cut[k_lo:k_hi], w1.w_cut[4 + k_lo:4 + k_hi]))))
+        x = torch.randn(5, shape.hidden, generator=torch.Generator().manual_seed(1))
+        mlp_ok = torch.allclose(mine._mlp(wr, x), one._mlp(w1, x), atol=1e-5)
+        attn_out = torch.randn(5, shape.n_q_heads * 128, generator=torch.Generator().manual_seed(2))
+        o_ok = torch.allclose(mine._all_reduce(attn_out[:, q_lo * 128:q_hi * 128] @ wr.wo), attn_out @ w1.wo, atol=1e-5)
+        lk1, lv1 = one._cutoffs(w1, rms_norm(x, w1.norm1, shape.rms_eps))
+        lkr, lvr = mine._cutoffs(wr, rms_norm(x, wr.norm1, shape.rms_eps))
+        cut_ok = torch.equal(lkr, lk1[:, k_lo:k_hi]) and torch.equal(lvr, lv1[:, k_lo:k_hi])
+        results[rank] = (cols_ok, mlp_ok, o_ok, cut_ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_runner_shards_by_kv_head_reproduce_the_one_rank_model():
+    port = _free_port()
+    with mp.Manager() as m:
+        results = m.dict()
+        mp.spawn(_runner_worker, args=(port, results), nprocs=WORLD, join=True)
+        for rank in range(WORLD):
+            assert results[rank] == (True, True, True, True), (rank, results[rank])

@@ -125,7 +125,10 @@ def workload_config(name, w, world, retention=None, bytes_step=None):
     if retention is not None:
         cfg["retention"] = retention
     if bytes_step is not None:
-        cfg["l2"] = "inputs larger than L2 (%.1f GB of distinct cache bytes per step per GPU), no flush" % (bytes_step / 1e9)
+        if bytes_step > 2 * 126e6:
+            cfg["l2"] = "inputs larger than L2 (%.1f GB of distinct cache bytes per step per GPU), no flush" % (bytes_step / 1e9)
+        else:   # a latency-bound side workload: its bytes stay in the 126 MB L2 from step to step
+            cfg["l2"] = "inputs smaller than L2 (%.0f MB per step per GPU) and not flushed: an L2-resident, latency-bound number" % (bytes_step / 1e6)
     return cfg
 
 

@@ -41,7 +41,10 @@ def two_stage_attention_noalloc(q, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_
     """``two_stage_attention`` for processes that must not allocate device memory while serving: the
     caller passes the output tensor, and the split partials go to a fixed 2 MiB array inside the library
     instead of a torch workspace.  Raises when the call needs more scratch than that (large batches) or when
-    the cache does not qualify for the split tensor-core path.  Calls on one device must not overlap."""
+    the cache does not qualify for the split tensor-core path.  Calls on one device must not overlap.
+    It is the library call that allocates nothing: this wrapper still creates the device status word with torch
+    on its first use on a device (and small fp32 copies when ``k_norm_weight`` is not fp32 already), so call it
+    once before the section that must not allocate."""
     q3 = q.squeeze(2) if q.dim() == 4 else q
     args, keep = build_attn_args(q3, k_flat, k_up, v_flat, v_up, l_k, o_k, l_v, o_v, theta, out=out,
                                  seq_lens=seq_lens, batch_index=batch_index, k_norm_weight=k_norm_weight,

@@ -126,8 +126,9 @@ int dkv_two_stage_decode(const dkv_attn_args* a);
  *  - DKV_E_LIMIT when the call needs more scratch than the array holds (the message gives both sizes):
  *    roughly groups * (batch + SMs/groups) * 2080 bytes, i.e. about 100 batch rows with 8 KV heads on a 148-SM GPU;
  *    DKV_E_ARG when the cache does not qualify for the split path (nothing is computed).
- *  - The first call on a device looks the array's address up (cudaGetSymbolAddress) and sets the
- *    kernel's shared-memory attribute; make that first call outside any stream capture.
+ *  - The first call on a device looks the array's address up (cudaGetSymbolAddress); make that first call
+ *    outside any stream capture.  Every call sets the kernels' shared-memory attribute (cudaFuncSetAttribute,
+ *    a host-side setting that allocates nothing), as dkv_two_stage_decode does.
  *  - All calls on a device share the array.  Nothing in it has to be cleared between calls (every record
  *    that is read was written by the same call), but two calls that overlap on the GPU -- different
  *    streams, or graph branches -- race on it: keep calls on one device ordered. */

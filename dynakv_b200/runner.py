@@ -122,6 +122,7 @@ class MiniLlama:
         self.batch = 0
         self.seq_lens_host: List[int] = []
         self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._segments: list = []
         self._ids: Optional[torch.Tensor] = None
         self._next: Optional[torch.Tensor] = None
 
@@ -199,61 +200,122 @@ class MiniLlama:
         return (last @ self.lm_head).argmax(dim=-1)
 
     # ------------------------------------------------------------------ one generated token
-    def _decode_layers(self, ids: torch.Tensor) -> torch.Tensor:
-        s, D, B = self.shape, self.shape.head_dim, ids.shape[0]
-        h = self.embed[ids]                                    # [B, H]
+    def _attention_part(self, li: int, h: torch.Tensor) -> torch.Tensor:
+        """Layer ``li`` from the residual stream to this rank's partial sum of the output projection [B, H]."""
+        s, D, B = self.shape, self.shape.head_dim, h.shape[0]
+        w = self.layers[li]
         has_short = any(n + 1 < self.policy.switch_tokens for n in self.seq_lens_host)
-        has_long = True                                        # rows only grow; keep the long kernels available
-        both = has_short and has_long
-        for li, w in enumerate(self.layers):
-            counter = self.cache.seq_lens(li)                  # tokens stored per row = position of the new token
-            cap = self.cache.key_cache_sp[li][1].shape[1]
-            x = rms_norm(h, w.norm1, s.rms_eps)
-            q = rope((x @ w.wq).view(B, self.q_local, D), counter, s.theta)
-            new_k = (x @ w.wk).view(B, self.kv_local, D)       # pre-RoPE: the append projects them onto the bases
-            new_v = (x @ w.wv).view(B, self.kv_local, D)
-            len_k, len_v = self._cutoffs(w, x)
-            out = torch.empty(B, self.q_local, D, dtype=self.dtype, device=self.device)
-            layer = self.attn[li]
-            layer.append(self.cache, new_k, new_v, len_k, len_v, counter, cap)
-            if has_short:
-                layer.attend(self.cache, q, out, counter, cap, "short_fused",
-                             route_max_tokens=self.policy.switch_tokens if both else 0)
-            layer.attend(self.cache, q, out, counter, cap, "long_two_stage",
-                         route_min_tokens=self.policy.switch_tokens if both else 0)
-            if self.trace is not None:
-                self.trace.append((li, q.clone(), out.clone()))
-            h = h + self._all_reduce(out.view(B, -1) @ w.wo)
-            h = h + self._mlp(w, rms_norm(h, w.norm2, s.rms_eps))
-        return (rms_norm(h, self.final_norm, s.rms_eps) @ self.lm_head)
+        counter = self.cache.seq_lens(li)                  # tokens stored per row = position of the new token
+        cap = self.cache.key_cache_sp[li][1].shape[1]
+        x = rms_norm(h, w.norm1, s.rms_eps)
+        q = rope((x @ w.wq).view(B, self.q_local, D), counter, s.theta)
+        new_k = (x @ w.wk).view(B, self.kv_local, D)       # pre-RoPE: the append projects them onto the bases
+        new_v = (x @ w.wv).view(B, self.kv_local, D)
+        len_k, len_v = self._cutoffs(w, x)
+        out = torch.empty(B, self.q_local, D, dtype=self.dtype, device=self.device)
+        layer = self.attn[li]
+        layer.append(self.cache, new_k, new_v, len_k, len_v, counter, cap)
+        if has_short:     # rows only grow: the long kernels are always there, the short one while a row needs it
+            layer.attend(self.cache, q, out, counter, cap, "short_fused", route_max_tokens=self.policy.switch_tokens)
+        layer.attend(self.cache, q, out, counter, cap, "long_two_stage",
+                     route_min_tokens=self.policy.switch_tokens if has_short else 0)
+        if self.trace is not None:
+            self.trace.append((li, q.clone(), out.clone()))
+        return out.view(B, -1) @ w.wo
+
+    def _mlp_part(self, li: int, h: torch.Tensor) -> torch.Tensor:
+        w = self.layers[li]
+        return (F.silu((x := rms_norm(h, w.norm2, self.shape.rms_eps)) @ w.wg) * (x @ w.wu)) @ w.wd
+
+    def _decode_layers(self, ids: torch.Tensor) -> torch.Tensor:
+        h = self.embed[ids]                                    # [B, H]
+        for li in range(len(self.layers)):
+            h = h + self._all_reduce(self._attention_part(li, h))
+            h = h + self._all_reduce(self._mlp_part(li, h))
+        return rms_norm(h, self.final_norm, self.shape.rms_eps) @ self.lm_head
+
+    # Tensor-parallel replay: the step is cut at its all-reduces.  Each piece between two all-reduces (a layer's
+    # attention part, a layer's MLP part, the head) is its own CUDA graph on static buffers; the all-reduces run
+    # eagerly between the replays, so no collective is ever captured.
+    def _capture_segments(self, ids: torch.Tensor) -> None:
+        B, H = ids.shape[0], self.shape.hidden
+        self._ids = ids.clone()
+        self._h = torch.zeros(B, H, dtype=self.dtype, device=self.device)
+        self._y = torch.zeros(B, H, dtype=self.dtype, device=self.device)
+        pool = torch.cuda.graph_pool_handle()
+        self._segments = []
+
+        def capture(fn):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                fn()
+            self._segments.append(g)
+
+        def first():
+            self._h.copy_(self.embed[self._ids])
+            self._y.copy_(self._attention_part(0, self._h))
+        capture(first)
+        for li in range(len(self.layers)):
+            def mlp(li=li):
+                self._h.add_(self._y)
+                self._y.copy_(self._mlp_part(li, self._h))
+            capture(mlp)
+            if li + 1 < len(self.layers):
+                def attn(li=li + 1):
+                    self._h.add_(self._y)
+                    self._y.copy_(self._attention_part(li, self._h))
+                capture(attn)
+
+        def head():
+            self._h.add_(self._y)
+            self.logits = rms_norm(self._h, self.final_norm, self.shape.rms_eps) @ self.lm_head
+            self._next = self.logits.argmax(dim=-1)
+        capture(head)
+
+    def _replay_segments(self) -> None:
+        last = len(self._segments) - 1
+        for i, g in enumerate(self._segments):
+            g.replay()
+            if i < last:
+                self._all_reduce(self._y)
+
+    def _dry_pass(self, ids: torch.Tensor) -> None:
+        """One eager step that sizes every workspace, with its effect on the caches' counters undone."""
+        for layer in self.attn:
+            layer.prepare(ids.shape[0], self.device)
+        snap = [(self.cache.seq_lens(li).clone(), self.cache.key_cache_sp[li][3].clone(),
+                 self.cache.value_cache_sp[li][3].clone()) for li in range(len(self.layers))]
+        self._decode_layers(ids)
+        torch.cuda.synchronize(self.device)
+        for li, (c, pk, pv) in enumerate(snap):
+            self.cache.seq_lens(li).copy_(c)
+            self.cache.key_cache_sp[li][3].copy_(pk)
+            self.cache.value_cache_sp[li][3].copy_(pv)
 
     @torch.no_grad()
     def decode_step(self, ids: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
         """Append the token ``ids`` [B] to every row and return the next greedy token [B] (and keep the logits in
-        ``self.logits``).  With ``use_graph`` (single-rank models only) the step is captured once and replayed.  A
-        tensor-parallel rank always runs the step eagerly: a captured step with ``torch.distributed`` all-reduces
-        inside did not finish on two GPUs, and is not offered."""
-        if use_graph and self.tp_size == 1 and self.trace is None:
-            if self._graph is None:
-                self._ids = ids.clone()
-                for layer in self.attn:
-                    layer.prepare(ids.shape[0], self.device)
-                # a dry pass sizes the workspaces (it appends a token): undo its effect on the counters afterwards
-                snap = [(self.cache.seq_lens(li).clone(), self.cache.key_cache_sp[li][3].clone(),
-                         self.cache.value_cache_sp[li][3].clone()) for li in range(len(self.layers))]
-                self._decode_layers(self._ids)
-                torch.cuda.synchronize(self.device)
-                for li, (c, pk, pv) in enumerate(snap):
-                    self.cache.seq_lens(li).copy_(c)
-                    self.cache.key_cache_sp[li][3].copy_(pk)
-                    self.cache.value_cache_sp[li][3].copy_(pv)
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    self.logits = self._decode_layers(self._ids)
-                    self._next = self.logits.argmax(dim=-1)
-                self._graph = g
+        ``self.logits``).  With ``use_graph`` the step is captured once and replayed: as one CUDA graph on a single
+        rank, as one graph per piece between all-reduces on a tensor-parallel rank (the collectives stay eager; a
+        captured step with ``torch.distributed`` all-reduces inside did not finish on two GPUs and is not offered).
+        Rows only grow and the kernels route each row on the device, so one capture serves all later steps."""
+        if use_graph and self.trace is None:
+            if self._graph is None and not self._segments:
+                self._dry_pass(ids)
+                if self.tp_size == 1:
+                    self._ids = ids.clone()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        self.logits = self._decode_layers(self._ids)
+                        self._next = self.logits.argmax(dim=-1)
+                    self._graph = g
+                else:
+                    self._capture_segments(ids)
             self._ids.copy_(ids)
-            self._graph.replay()
+            if self._graph is not None:
+                self._graph.replay()
+            else:
+                self._replay_segments()
             nxt = self._next
         else:
             self.logits = self._decode_layers(ids)
@@ -316,7 +378,7 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
     ap.add_argument("--prompt", type=int, default=8192)
     ap.add_argument("--new-tokens", type=int, default=100)
     ap.add_argument("--mode", default="dp", choices=["dp", "tp"])
-    ap.add_argument("--graph", action="store_true", help="replay the decode step as a CUDA graph (dp only)")
+    ap.add_argument("--graph", action="store_true", help="replay the decode step from CUDA graphs (tp: one per piece between all-reduces)")
     ap.add_argument("--cutoff-bias", type=float, default=-1.25)
     args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -333,7 +395,7 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
     ids = torch.randint(0, shape.vocab, (args.batch, args.prompt), generator=gen, device=dev)
     if world > 1:
         dist.barrier()
-    res = decode_throughput(model, ids, args.new_tokens, use_graph=args.graph and not tp)
+    res = decode_throughput(model, ids, args.new_tokens, use_graph=args.graph)
     ms = res["ms_per_step"]
     kept = sum(float(c[1][:, : args.prompt].float().mean().item()) for c in model.cache.key_cache_sp) / shape.layers / 128
     if world > 1:
@@ -347,7 +409,7 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
                           "config": {"workload": "random-init Llama-shaped decode", "layers": shape.layers,
                                      "hidden": shape.hidden, "mlp": shape.mlp, "vocab": shape.vocab,
                                      "prompt": args.prompt, "new_tokens": args.new_tokens,
-                                     "decode_steps_timed": res["decode_steps_timed"], "cuda_graph": bool(args.graph and not tp)},
+                                     "decode_steps_timed": res["decode_steps_timed"], "cuda_graph": bool(args.graph)},
                           "prefill_ms": res["prefill_ms"], "key_retention_of_prompt": kept, "dtype": "bf16",
                           "data": "synthetic"}))
     if world > 1:

@@ -59,7 +59,7 @@ def test_generated_tokens_attend_like_the_oracle_and_the_graph_replays_the_eager
     assert _common.read_status(torch.device(DEV)) == 0
 
 
-def _tp_worker(rank, world, port, ids, new_tokens, out_path):
+def _tp_worker(rank, world, port, ids, new_tokens, out_path, use_graph):
     import os
 
     import torch.distributed as dist
@@ -71,7 +71,7 @@ def _tp_worker(rank, world, port, ids, new_tokens, out_path):
     nxt = model.prefill(ids.to(dev), new_tokens + 4)
     logits = []
     for _ in range(new_tokens):
-        nxt = model.decode_step(nxt.clone())
+        nxt = model.decode_step(nxt.clone(), use_graph=use_graph)
         logits.append(model.logits.float().cpu())
     if rank == 0:
         torch.save(torch.stack(logits), out_path)
@@ -80,15 +80,17 @@ def _tp_worker(rank, world, port, ids, new_tokens, out_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_sharded_by_kv_head_give_the_logits_of_one_rank(tmp_path):
+@pytest.mark.parametrize("use_graph", [False, True], ids=["eager", "graph-per-piece"])
+def test_two_ranks_sharded_by_kv_head_give_the_logits_of_one_rank(tmp_path, use_graph):
     """Tensor parallel by KV head on 2 GPUs (this package's kernels on each rank's heads, NCCL all-reduce after the
-    row-parallel output and down projections) against the same model on one GPU."""
+    row-parallel output and down projections) against the same model on one GPU; eagerly, and replayed from one
+    CUDA graph per piece between all-reduces."""
     import torch.multiprocessing as mp
     P, NEW = 520, 3
     gen = torch.Generator().manual_seed(3)
     ids = torch.randint(0, TINY.vocab, (2, P), generator=gen)
     out_path = str(tmp_path / "tp_logits.pt")
-    mp.spawn(_tp_worker, args=(2, 29533, ids, NEW, out_path), nprocs=2, join=True)
+    mp.spawn(_tp_worker, args=(2, 29533 + int(use_graph), ids, NEW, out_path, use_graph), nprocs=2, join=True)
     got = torch.load(out_path)
     model = MiniLlama(TINY, DEV, seed=5)
     nxt = model.prefill(ids.to(DEV), NEW + 4)

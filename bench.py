@@ -35,6 +35,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -351,6 +352,67 @@ def prefill_compress_leg(dev, reps=200):
                           "of_hbm_peak": 2 * payload / (ms_pack * 1e-3) / 1e9 / hbm, "retention": payload / (x.numel() * 2)}}
 
 
+def joint_layout_leg(dev):
+    """The reference's literal layout next to the headline: one joint latent row per batch row (R = 1024 over all
+    heads), bases [Hq, 1024, 128], any integer length (len_multiple 1).  It runs on the generic CUDA-core kernels
+    (the tensor-core kernels need per-KV-head arenas and lengths in multiples of 8); with the reference's own
+    Triton kernels on the same tensors beside it when the installed copy is there."""
+    from dynakv_b200.kernels.fused import fused_attention_dispatch
+    from dynakv_b200.kernels.two_stage import two_stage_attention
+    B, S, R = 2, 2048, 1024
+    gen = torch.Generator(device=dev).manual_seed(4017)
+    dt = torch.bfloat16
+
+    def side():
+        lens = torch.randint(1, 411, (B, S), generator=gen, device=dev, dtype=torch.int32)
+        offs = (torch.cumsum(lens.long(), 1) - lens.long()).to(torch.int32)
+        cap = (int(lens.long().sum(1).max().item()) + 7) // 8 * 8
+        sigma = torch.exp(-torch.arange(R, device=dev, dtype=torch.float32) / 256.0)
+        flat = torch.randn(B, cap, generator=gen, device=dev) * sigma[torch.arange(cap, device=dev) % R]
+        return flat.to(dt), lens, offs
+
+    fk, lk, ok = side()
+    fv, lv, ov = side()
+    k_up = (torch.randn(N_Q_HEADS, R, HEAD_DIM, generator=gen, device=dev) / math.sqrt(R)).to(dt)
+    v_up = (torch.randn(N_Q_HEADS, R, HEAD_DIM, generator=gen, device=dev) / math.sqrt(R)).to(dt)
+    q = torch.randn(B, N_Q_HEADS, HEAD_DIM, generator=gen, device=dev).to(dt)
+    theta = 500000.0
+    nbytes = float((lk.long().sum() + lv.long().sum()).item()) * 2
+
+    def timed(fn, reps=5):
+        out = fn(); fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return out, e0.elapsed_time(e1) / reps * 1e3
+
+    out2, us2 = timed(lambda: two_stage_attention(q, fk, k_up, fv, v_up, lk, ok, lv, ov, theta))
+    out1, us1 = timed(lambda: fused_attention_dispatch(q, fk, k_up, fv, v_up, lk, ok, lv, ov, theta))
+    res = {"workload": "joint latent rows, B=2, S=2048, R=1024, bases [32, 1024, 128], integer lengths 1..410, bf16",
+           "kernels": "generic CUDA-core kernels (len_multiple 1, one arena per batch row)",
+           "two_stage_us": us2, "fused_us": us1, "compressed_bytes": nbytes,
+           "two_stage_gbs": nbytes / (us2 * 1e-6) / 1e9,
+           "max_abs_two_stage_vs_fused": float((out2.float() - out1.float()).abs().max())}
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.isdir(os.path.join(ref_root, "dynakv")):
+        try:
+            sys.path.insert(0, ref_root)
+            from dynakv.kernels.two_stage import abx_sparse, avx
+            ref_out, ref_us = timed(lambda: avx(abx_sparse(q, k_up, fk, lk, offsets=ok, theta=theta), fv, v_up, lv, ov), reps=3)
+            res["reference_triton_us"] = ref_us
+            res["max_abs_vs_reference_triton"] = float((ref_out.float() - out2.float()).abs().max())
+        except Exception as exc:
+            res["reference_triton_unavailable"] = "%s: %s" % (type(exc).__name__, str(exc)[:160])
+        finally:
+            if sys.path and sys.path[0] == ref_root:
+                sys.path.pop(0)
+    return res
+
+
 def tensor_pipe_probe(dev, tiles=100):
     """Cycles per 128-token tile that one SM's tensor pipe is held by the decode kernel's three tcgen05.mma chains
     (issued back to back by one thread, nothing else on the SM): the floor under the split kernel's time per tile."""
@@ -565,6 +627,7 @@ def run_ours(args):
         line["gpu_reference"] = gpu_ref
     if prefill is not None:
         line["prefill_compress"] = prefill
+        line["joint_layout"] = joint_layout_leg(dev)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_reference(w, steps=20, warmup=2)
     print(json.dumps(line), flush=True)

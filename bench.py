@@ -393,7 +393,8 @@ def joint_layout_leg(dev):
     out2, us2 = timed(lambda: two_stage_attention(q, fk, k_up, fv, v_up, lk, ok, lv, ov, theta))
     out1, us1 = timed(lambda: fused_attention_dispatch(q, fk, k_up, fv, v_up, lk, ok, lv, ov, theta))
     res = {"workload": "joint latent rows, B=2, S=2048, R=1024, bases [32, 1024, 128], integer lengths 1..410, bf16",
-           "kernels": "generic CUDA-core kernels (len_multiple 1, one arena per batch row)",
+           "kernels": "generic kernels (len_multiple 1, one arena per batch row): mma.sync K reconstruction, "
+                      "two-stage entry split over the token axis",
            "two_stage_us": us2, "fused_us": us1, "compressed_bytes": nbytes,
            "two_stage_gbs": nbytes / (us2 * 1e-6) / 1e9,
            "max_abs_two_stage_vs_fused": float((out2.float() - out1.float()).abs().max())}

@@ -30,6 +30,8 @@ int sm_count() {
 // implemented in dkv_generic.cu / dkv_mma_decode.cu
 int check_attn_args(const dkv_attn_args* a, const char* who, bool need_q, bool need_k, bool need_v);
 int generic_attention(const dkv_attn_args* a);
+int generic_two_stage(const dkv_attn_args* a);
+size_t generic_split_workspace_bytes(const dkv_attn_args* a);
 bool mma_path_ok(const dkv_attn_args* a);
 size_t mma_split_workspace_bytes(const dkv_attn_args* a);
 int mma_fused(const dkv_attn_args* a);
@@ -52,7 +54,8 @@ extern "C" int dkv_fused_decode(const dkv_attn_args* a) {
 }
 
 extern "C" size_t dkv_split_workspace_bytes(const dkv_attn_args* a) {
-  if (a == nullptr || !mma_path_ok(a)) return 0;
+  if (a == nullptr) return 0;
+  if (!mma_path_ok(a)) return generic_split_workspace_bytes(a);
   return mma_split_workspace_bytes(a);
 }
 
@@ -73,7 +76,7 @@ extern "C" int dkv_split_combine(const dkv_attn_args* a) {
 
 extern "C" int dkv_two_stage_decode(const dkv_attn_args* a) {
   if (int rc = check_attn_args(a, "dkv_two_stage_decode", true, true, true)) return rc;
-  if (!mma_path_ok(a)) return generic_attention(a);
+  if (!mma_path_ok(a)) return generic_two_stage(a);
   if (int rc = mma_split(a)) return rc;
   return mma_combine(a);
 }

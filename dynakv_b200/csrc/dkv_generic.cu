@@ -13,11 +13,15 @@
 //   softmax over s, accumulate sum_s p_s x^v_s in latent space, project once through Bv[g].
 #include <math.h>
 
+#include <type_traits>
+
 #include "dkv_common.cuh"
 
 namespace dkv {
 
-enum { MODE_ATTN = 0, MODE_SCORES = 1, MODE_SOFTMAX_V = 2 };
+enum { MODE_ATTN = 0, MODE_SCORES = 1, MODE_SOFTMAX_V = 2, MODE_ATTN_SPLIT = 3 };
+// MODE_ATTN_SPLIT: blockIdx.z takes a slice of the tokens and leaves a partial record (m, l, latent accumulator) in
+// the workspace; generic_combine_kernel merges the records of a (row, head) and projects through Bv.
 
 constexpr int GD = 128;       // head_dim
 constexpr int GTT = 32;       // tokens per tile
@@ -27,10 +31,14 @@ constexpr int GZ_TOKENS = 256;  // tokens per blockIdx.z slice in MODE_SCORES
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(GTHREADS)
-generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t sc_sb, int64_t sc_sh, float log_theta) {
+generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t sc_sb, int64_t sc_sh, float log_theta,
+                      int split_tokens) {
   __shared__ float q_s[GD];
   __shared__ float k_s[GTT][GD + 1];
-  __shared__ float x_s[GTT][GRC];
+  // staging: fp32 path = x tile [GTT][GRC] floats; 16-bit path = x tile [GTT][GRC + 8] and basis chunk
+  // [GRC][GD + 8] in the storage type (row pitches of 144 and 272 bytes keep ldmatrix free of bank conflicts)
+  __shared__ __align__(16) unsigned char stage_raw[GTT * (GRC + 8) * 2 + GRC * (GD + 8) * 2];
+  float (*x_s)[GRC] = reinterpret_cast<float (*)[GRC]>(stage_raw);
   __shared__ float sc_s[GTT], p_s[GTT];
   __shared__ int lenk_s[GTT], offk_s[GTT], lenv_s[GTT], offv_s[GTT];
   __shared__ float alpha_s, l_s;
@@ -42,13 +50,17 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
   const int A = p.arenas_per_batch, Hq = p.n_q_heads, R = p.rank;
   const int g = h / (Hq / p.n_basis_groups);
   const int a = b * A + (h * A) / Hq;
-  if (MODE == MODE_ATTN && row_routed_out(p, b)) return;   // the row belongs to the other kernel
+  if ((MODE == MODE_ATTN || MODE == MODE_ATTN_SPLIT) && row_routed_out(p, b)) return;   // the row belongs to the other kernel
   int S = p.seq_len;
   if (p.seq_lens) S = min(S, max(p.seq_lens[b], 0));
   int t_begin = 0, t_end = S;
   if (MODE == MODE_SCORES) {
     t_begin = blockIdx.z * GZ_TOKENS;
     t_end = min(p.seq_len, t_begin + GZ_TOKENS);  // scores are written for every column
+  }
+  if (MODE == MODE_ATTN_SPLIT) {
+    t_begin = min(S, (int)blockIdx.z * split_tokens);
+    t_end = min(S, t_begin + split_tokens);
   }
 
   const T* kflat = reinterpret_cast<const T*>(p.k.flat) + (size_t)a * p.k.flat_stride;
@@ -103,26 +115,102 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
 
     if (MODE != MODE_SOFTMAX_V) {
       // ---- K reconstruction: k[t][d] = sum_r x[t][r] * Bk[r][d] ----
-      float acc[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) acc[i] = 0.f;
       const int rmax = rmax_s;
-      for (int r0 = 0; r0 < rmax; r0 += GRC) {
-        for (int e = tid; e < GTT * GRC; e += GTHREADS) {
-          const int t = e / GRC, rr = e - t * GRC, r = r0 + rr;
-          x_s[t][rr] = (r < lenk_s[t]) ? to_f32(kflat[(size_t)offk_s[t] + r]) : 0.f;
-        }
-        __syncthreads();
-        const int nr = min(GRC, rmax - r0);
-        for (int rr = 0; rr < nr; ++rr) {
-          const float bv = to_f32(kup[(size_t)(r0 + rr) * GD + d]);
+      if constexpr (sizeof(T) == 2) {
+        // 16-bit storage: mma.sync m16n8k16 with fp32 accumulation (what the reference's tl.dot does); warp w owns
+        // output dims 16w..16w+15 of all 32 tokens
+        T (*xs)[GRC + 8] = reinterpret_cast<T (*)[GRC + 8]>(stage_raw);
+        T (*bs)[GD + 8] = reinterpret_cast<T (*)[GD + 8]>(stage_raw + GTT * (GRC + 8) * 2);
+        const bool vec = (reinterpret_cast<uintptr_t>(p.k_up) & 15) == 0;
+        float acc[2][2][4];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[i] = fmaf(x_s[th * 16 + i][rr], bv, acc[i]);
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+        for (int r0 = 0; r0 < rmax; r0 += GRC) {
+          for (int e = tid; e < GTT * GRC; e += GTHREADS) {
+            const int t = e / GRC, rr = e - t * GRC, r = r0 + rr;
+            xs[t][rr] = (r < lenk_s[t]) ? kflat[(size_t)offk_s[t] + r] : from_f32<T>(0.f);
+          }
+          for (int e = tid; e < GRC * (GD / 8); e += GTHREADS) {
+            const int rr = e >> 4, c = e & 15, r = r0 + rr;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < R) {
+              if (vec) {
+                v = __ldg(reinterpret_cast<const uint4*>(kup + (size_t)r * GD) + c);
+              } else {
+                T tmp[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) tmp[i] = kup[(size_t)r * GD + 8 * c + i];
+                v = *reinterpret_cast<const uint4*>(tmp);
+              }
+            }
+            *reinterpret_cast<uint4*>(&bs[rr][8 * c]) = v;
+          }
+          __syncthreads();
+          const int ksteps = (min(GRC, rmax - r0) + 15) >> 4;
+          for (int ks = 0; ks < ksteps; ++ks) {
+            uint32_t af[2][4], bf[4];
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+              const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&xs[16 * m + (lane & 15)][16 * ks + 8 * (lane >> 4)]);
+              asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(af[m][0]), "=r"(af[m][1]), "=r"(af[m][2]), "=r"(af[m][3]) : "r"(addr));
+            }
+            {
+              const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&bs[16 * ks + (lane & 15)][16 * warp + 8 * (lane >> 4)]);
+              asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(bf[0]), "=r"(bf[1]), "=r"(bf[2]), "=r"(bf[3]) : "r"(addr));
+            }
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+              for (int n = 0; n < 2; ++n) {
+                if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+                  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                               : "+f"(acc[m][n][0]), "+f"(acc[m][n][1]), "+f"(acc[m][n][2]), "+f"(acc[m][n][3])
+                               : "r"(af[m][0]), "r"(af[m][1]), "r"(af[m][2]), "r"(af[m][3]), "r"(bf[2 * n]), "r"(bf[2 * n + 1]));
+                } else {
+                  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                               : "+f"(acc[m][n][0]), "+f"(acc[m][n][1]), "+f"(acc[m][n][2]), "+f"(acc[m][n][3])
+                               : "r"(af[m][0]), "r"(af[m][1]), "r"(af[m][2]), "r"(af[m][3]), "r"(bf[2 * n]), "r"(bf[2 * n + 1]));
+                }
+              }
+          }
+          __syncthreads();
         }
-        __syncthreads();
+        const int gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+          for (int n = 0; n < 2; ++n) {
+            const int row = 16 * m + gq, col = 16 * warp + 8 * n + 2 * tq;
+            k_s[row][col] = acc[m][n][0]; k_s[row][col + 1] = acc[m][n][1];
+            k_s[row + 8][col] = acc[m][n][2]; k_s[row + 8][col + 1] = acc[m][n][3];
+          }
+      } else {
+        float acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+        for (int r0 = 0; r0 < rmax; r0 += GRC) {
+          for (int e = tid; e < GTT * GRC; e += GTHREADS) {
+            const int t = e / GRC, rr = e - t * GRC, r = r0 + rr;
+            x_s[t][rr] = (r < lenk_s[t]) ? to_f32(kflat[(size_t)offk_s[t] + r]) : 0.f;
+          }
+          __syncthreads();
+          const int nr = min(GRC, rmax - r0);
+          for (int rr = 0; rr < nr; ++rr) {
+            const float bv = to_f32(kup[(size_t)(r0 + rr) * GD + d]);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(x_s[th * 16 + i][rr], bv, acc[i]);
+          }
+          __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) k_s[th * 16 + i][d] = acc[i];
       }
-#pragma unroll
-      for (int i = 0; i < 16; ++i) k_s[th * 16 + i][d] = acc[i];
       __syncthreads();
 
       // ---- optional RMSNorm, RoPE, q.k : one warp per token ----
@@ -201,6 +289,18 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
   }
 
   if (MODE == MODE_SCORES) return;
+  if (MODE == MODE_ATTN_SPLIT) {
+    // partial record of this slice: [m, l, acc[R]] at ((row, head), slice)
+    float* rec = reinterpret_cast<float*>(p.workspace) +
+                 (((size_t)blockIdx.x * Hq + h) * gridDim.z + blockIdx.z) * (size_t)(2 + R);
+    if (tid == 0) { rec[0] = m_run; rec[1] = l_s; }      // warp 0 owns the running maximum
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = tid + i * GTHREADS;
+      if (r < R) rec[2 + r] = acc_lat[i];
+    }
+    return;
+  }
 
   // ---- normalise and project the latent accumulator through Bv ----
   float* lat_s = &k_s[0][0];  // >= 1024 floats
@@ -228,6 +328,73 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
     T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)h * p.out_stride_h;
     op[d] = from_f32<T>(o + o1);
   }
+}
+
+// Merge the slices' partial records of one (row, head) and project through Bv (MODE_ATTN_SPLIT's second half).
+template <typename T>
+__global__ void __launch_bounds__(GTHREADS) generic_combine_kernel(dkv_attn_args p, int n_split) {
+  __shared__ float lat_s[1024];
+  __shared__ float w_s[64];
+  __shared__ float half_s[GD];
+  __shared__ float L_s;
+  const int tid = threadIdx.x, h = blockIdx.y, Hq = p.n_q_heads, R = p.rank;
+  const int b = p.batch_index ? p.batch_index[blockIdx.x] : blockIdx.x;
+  if (row_routed_out(p, b)) return;
+  const int g = h / (Hq / p.n_basis_groups);
+  const float* rec0 = reinterpret_cast<const float*>(p.workspace) + (((size_t)blockIdx.x * Hq + h) * n_split) * (size_t)(2 + R);
+  if (tid < 32) {
+    float M = -INFINITY;
+    for (int k = tid; k < n_split; k += 32) M = fmaxf(M, rec0[(size_t)k * (2 + R)]);
+    M = warp_max(M);
+    float L = 0.f;
+    for (int k = tid; k < n_split; k += 32) {
+      const float m = rec0[(size_t)k * (2 + R)];
+      const float w = (m == -INFINITY) ? 0.f : __expf(m - M);
+      w_s[k] = w;
+      L = fmaf(w, rec0[(size_t)k * (2 + R) + 1], L);
+    }
+    L = warp_sum(L);
+    if (tid == 0) L_s = L;
+  }
+  __syncthreads();
+  const float L = L_s;
+  if (L <= 0.f && tid == 0) set_status(p.status, DKV_ST_EMPTY_ROW);
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int r = tid; r < R; r += GTHREADS) {
+    float v = 0.f;
+    for (int k = 0; k < n_split; ++k)
+      if (w_s[k] != 0.f) v = fmaf(w_s[k], rec0[(size_t)k * (2 + R) + 2 + r], v);
+    lat_s[r] = v * inv;
+  }
+  __syncthreads();
+  const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * GD;
+  const int d = tid & (GD - 1), th = tid >> 7;
+  const int r_half = (R + 1) / 2, r_lo = th * r_half, r_hi = min(R, r_lo + r_half);
+  float o = 0.f;
+  for (int r = r_lo; r < r_hi; ++r) o = fmaf(lat_s[r], to_f32(vup[(size_t)r * GD + d]), o);
+  if (th == 1) half_s[d] = o;
+  __syncthreads();
+  if (th == 0) {
+    T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)h * p.out_stride_h;
+    op[d] = from_f32<T>(o + half_s[d]);
+  }
+}
+
+// Slices of the token axis for the two-stage entry on caches that take this path: at least 256 tokens each, at most 64.
+static int generic_split_tokens(const dkv_attn_args* a) {
+  int t = (a->seq_len + 63) / 64;
+  t = (t + GTT - 1) / GTT * GTT;
+  return t < 256 ? 256 : t;
+}
+static int generic_n_split(const dkv_attn_args* a) {
+  const int t = generic_split_tokens(a);
+  const int n = (a->seq_len + t - 1) / t;
+  return n < 1 ? 1 : n;
+}
+size_t generic_split_workspace_bytes(const dkv_attn_args* a) {
+  const int n = generic_n_split(a);
+  if (n <= 1) return 0;
+  return (size_t)a->batch * a->n_q_heads * n * (size_t)(2 + a->rank) * sizeof(float);
 }
 
 int check_attn_args(const dkv_attn_args* a, const char* who, bool need_q, bool need_k, bool need_v) {
@@ -260,18 +427,39 @@ static int launch_generic(const dkv_attn_args* a, const void* scores, int64_t sb
     DKV_REQUIRE(grid.z <= 65535, DKV_E_LIMIT, "dkv_scores: seq_len too large");
   }
   const float log_theta = (float)log((double)a->theta);
+  int split_tokens = 0, n_split = 1;
+  if (MODE == MODE_ATTN_SPLIT) {
+    split_tokens = generic_split_tokens(a);
+    n_split = generic_n_split(a);
+    grid.z = n_split;
+  }
   if (a->dtype == DKV_F32)
-    generic_decode_kernel<float, MODE><<<grid, GTHREADS, 0, st>>>(*a, (const float*)scores, sb, sh, log_theta);
+    generic_decode_kernel<float, MODE><<<grid, GTHREADS, 0, st>>>(*a, (const float*)scores, sb, sh, log_theta, split_tokens);
   else if (a->dtype == DKV_F16)
-    generic_decode_kernel<__half, MODE><<<grid, GTHREADS, 0, st>>>(*a, (const __half*)scores, sb, sh, log_theta);
+    generic_decode_kernel<__half, MODE><<<grid, GTHREADS, 0, st>>>(*a, (const __half*)scores, sb, sh, log_theta, split_tokens);
   else
     generic_decode_kernel<__nv_bfloat16, MODE><<<grid, GTHREADS, 0, st>>>(*a, (const __nv_bfloat16*)scores, sb, sh,
-                                                                        log_theta);
+                                                                        log_theta, split_tokens);
   DKV_CHECK_LAUNCH();
+  if (MODE == MODE_ATTN_SPLIT) {
+    const dim3 cgrid(a->batch, a->n_q_heads);
+    if (a->dtype == DKV_F32) generic_combine_kernel<float><<<cgrid, GTHREADS, 0, st>>>(*a, n_split);
+    else if (a->dtype == DKV_F16) generic_combine_kernel<__half><<<cgrid, GTHREADS, 0, st>>>(*a, n_split);
+    else generic_combine_kernel<__nv_bfloat16><<<cgrid, GTHREADS, 0, st>>>(*a, n_split);
+    DKV_CHECK_LAUNCH();
+  }
   return DKV_OK;
 }
 
 int generic_attention(const dkv_attn_args* a) { return launch_generic<MODE_ATTN>(a, nullptr, 0, 0); }
+
+// Two-stage entry on this path: slices of the token axis + merge when the caller's workspace holds the records,
+// one CTA per (row, head) otherwise.
+int generic_two_stage(const dkv_attn_args* a) {
+  const size_t need = generic_split_workspace_bytes(a);
+  if (need == 0 || a->workspace == nullptr || a->workspace_bytes < need) return generic_attention(a);
+  return launch_generic<MODE_ATTN_SPLIT>(a, nullptr, 0, 0);
+}
 
 }  // namespace dkv
 

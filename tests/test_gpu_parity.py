@@ -108,6 +108,45 @@ def test_16bit_joint_layout_of_the_reference(fn, dtype):
     _check16(_run(fn, t, float(g["theta"])), ref)
 
 
+def _joint_case(seed, B, S, R, Hq, dtype, ragged=False):
+    """The reference's literal layout: one joint latent row per batch row, bases [Hq, R, 128], any integer length."""
+    gen = torch.Generator().manual_seed(seed)
+
+    def side():
+        lens = torch.randint(0, R // 2, (B, S), generator=gen, dtype=torch.int32)
+        lens[:, 0] = torch.maximum(lens[:, 0], torch.ones_like(lens[:, 0]))
+        offs = (torch.cumsum(lens.long(), 1) - lens.long()).to(torch.int32)
+        cap = int(lens.long().sum(1).max()) + 5
+        sigma = torch.exp(-torch.arange(R, dtype=torch.float32) / (R / 4))
+        flat = (torch.randn(B, cap, generator=gen) * sigma[torch.arange(cap) % R]).to(dtype)
+        return flat, lens, offs
+
+    fk, lk, ok = side()
+    fv, lv, ov = side()
+    t = {"q": torch.randn(B, Hq, 128, generator=gen).to(dtype), "flat_k": fk, "flat_v": fv, "lens_k": lk, "lens_v": lv,
+         "offs_k": ok, "offs_v": ov,
+         "k_up": (torch.randn(Hq, R, 128, generator=gen) / R ** 0.5).to(dtype),
+         "v_up": (torch.randn(Hq, R, 128, generator=gen) / R ** 0.5).to(dtype)}
+    return t
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "fp16", "fp32"])
+def test_joint_layout_long_cache_slices_and_merges(dtype):
+    # 700 tokens: the two-stage entry cuts the token axis into slices and merges their partial records; the 16-bit
+    # types reconstruct K with mma.sync.  Ragged rows (300 and 700 tokens) leave one row's last slices empty.
+    t = _joint_case(21, 2, 700, 256, 8, dtype)
+    seq = [300, 700]
+    ref = _oracle(t, 10000.0, seq_lens=seq)
+    sl = torch.tensor(seq, dtype=torch.int32, device=DEV)
+    for fn in (two_stage_attention, fused_attention_dispatch):
+        out = _run(fn, t, 10000.0, seq_lens=sl)
+        if dtype == torch.float32:
+            assert float((out.cpu() - ref).abs().max()) < 5e-5
+            assert _common.read_status(torch.device(DEV)) == 0
+        else:
+            _check16(out, ref)
+
+
 @pytest.mark.parametrize("fn", [fused_attention_dispatch, two_stage_attention])
 def test_qwen_knorm_bf16(fn):
     g, t = _golden_attn("attn_qwen_knorm_s50", torch.bfloat16)

@@ -386,6 +386,8 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # NCCL prints its version banner (and any NCCL_DEBUG output) on stdout; stdout carries the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     shape = ModelShape(layers=args.layers, hidden=args.hidden, mlp=args.mlp, vocab=args.vocab)
     tp = args.mode == "tp"

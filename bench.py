@@ -496,8 +496,11 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL prints its version banner (and any NCCL_DEBUG output) on stdout; stdout carries the one JSON line
+        # stdout carries the one JSON line: NCCL's debug output goes to stderr, and the version banner, which NCCL
+        # prints on stdout at debug level VERSION whatever the debug file is, is switched off
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     from dynakv_b200 import _lib
     from dynakv_b200.kernels import _common

@@ -271,17 +271,27 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
       __syncthreads();
       // every thread tracks the running max through alpha only; warp 0 owns m_run
       const float alpha = alpha_s;
-      // ---- latent-space V accumulation ----
+      // ---- latent-space V accumulation: thread owns latent indices tid + 256 i; eight tokens' loads in flight ----
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = tid + i * GTHREADS;
-        if (r < R) {
-          float accv = acc_lat[i] * alpha;
-          for (int t = 0; t < GTT; ++t) {
-            const float pv = p_s[t];
-            if (pv != 0.f && r < lenv_s[t]) accv = fmaf(pv, to_f32(vflat[(size_t)offv_s[t] + r]), accv);
+      for (int i = 0; i < 4; ++i) acc_lat[i] *= alpha;
+      for (int tb = 0; tb < GTT; tb += 8) {
+        float v[4][8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int t = tb + u;
+          const int lv = p_s[t] != 0.f ? lenv_s[t] : 0;
+          const T* row = vflat + (size_t)offv_s[t];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = tid + i * GTHREADS;
+            v[i][u] = r < lv ? to_f32(row[r]) : 0.f;     // lv <= R
           }
-          acc_lat[i] = accv;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float pv = p_s[tb + u];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc_lat[i] = fmaf(pv, v[i][u], acc_lat[i]);
         }
       }
       __syncthreads();

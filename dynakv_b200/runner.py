@@ -386,8 +386,11 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # NCCL prints its version banner (and any NCCL_DEBUG output) on stdout; stdout carries the one JSON line
+        # stdout carries the one JSON line: NCCL's debug output goes to stderr, and the version banner, which NCCL
+        # prints on stdout at debug level VERSION whatever the debug file is, is switched off
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     shape = ModelShape(layers=args.layers, hidden=args.hidden, mlp=args.mlp, vocab=args.vocab)
     tp = args.mode == "tp"

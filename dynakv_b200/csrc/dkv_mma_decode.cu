@@ -195,6 +195,26 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same instructions with the operand descriptors passed as two 32-bit words: the issuer threads keep the words
+// of each ring slot ready and add the (compile-time) k-step offset to the low word, so that nothing but that add
+// stands between two tcgen05.mma of a product -- the descriptor arithmetic of umma_desc (shifts, masks and 64-bit
+// ors, ~15 dependent instructions per product step on a lone thread) was what an issue block waited on.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo) { return ((addr >> 4) & 0x3FFFu) | (((lbo >> 4) & 0x3FFFu) << 16); }
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo) { return ((sbo >> 4) & 0x3FFFu) | (1u << 14); }
+__device__ __forceinline__ void umma_f16_w(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .b64 da, db;\n.reg .pred p;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\nsetp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ta_w(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .b64 db;\n.reg .pred p;\nmov.b64 db, {%2, %3};\nsetp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -604,7 +624,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;   // 0 = f16, 1 = bf16
       const uint32_t idesc_k = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
       const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-      const uint32_t basis_addr = smem_u32(sm.basis);
+      // descriptor words: low = (address >> 4) | (LBO >> 4) << 16, high = (SBO >> 4) | version bit
+      const uint32_t a_lo0 = desc_lo(smem_u32(sm.a_tile[0]), 2048), b_lo0 = desc_lo(smem_u32(sm.basis), 2048);
+      const uint32_t q_lo0 = desc_lo(smem_u32(sm.qrot[0]), Q_LBO), hi_128 = desc_hi(128);
+      static_assert(TILE_BYTES % 16 == 0 && Q_TILE_BYTES % 16 == 0 && (2 * Q_LBO) % 16 == 0, "descriptor steps are whole 16-byte units");
       int ri = 0, qi = 0;     // next tile of products (1), (2)
       int rt = 0, qt = 0;     // their accumulator buffers ri % 3, qi % 3 ...
       uint32_t rtp = 0, qtp = 0;   // ... and phases (ri / 3) & 1, (qi / 3) & 1
@@ -620,13 +643,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         if (ri < n_stages && ri - qi < NBUF_T && r_ok) {
           proxy_fence_async();   // the tile was written by cp.async (generic proxy), the tensor core reads it through the async proxy
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sm.a_tile[rb]);
+          const uint32_t a_lo = a_lo0 + (uint32_t)rb * (TILE_BYTES >> 4), d_k = tmem_base + TM_K + rt * 128;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             // A: K-major, 8-row core matrices 128 B apart (SBO), the two 8-coefficient chunks 2048 B apart (LBO)
             // B: MN-major, 8-column core matrices 128 B apart (SBO), the two 8-row groups 2048 B apart (LBO)
-            umma_f16(tmem_base + TM_K + rt * 128, umma_desc(a_addr + ks * 4096, 2048, 128),
-                     umma_desc(basis_addr + ks * 4096, 2048, 128), idesc_k, ks > 0 ? 1u : 0u);
+            // a k-step is 4096 B further in both tiles
+            umma_f16_w(d_k, a_lo + ks * 256, hi_128, b_lo0 + ks * 256, hi_128, idesc_k, ks > 0 ? 1u : 0u);
           }
           umma_commit(smem_u32(&sm.t_ready[rt]));   // also frees the operand tile (the K gather warps wait on it too)
           ++ri;
@@ -635,15 +658,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         }
         if (qi < ri && k_ok && q_ok && !(progress && qi + 1 == ri)) {
           tc_fence_after();
-          const uint32_t q_addr = smem_u32(sm.qrot[qg]);
+          const uint32_t q_lo = q_lo0 + (uint32_t)qg * (Q_TILE_BYTES >> 4), d_s = tmem_base + TM_S + 16 * qg;
           const uint32_t kp = tmem_base + TM_K + qt * 128;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             // A: K' of the tile, dims 16ks..16ks+15 = 8 packed columns; each 32-dim quarter of the row starts its
             // 16 packed columns at the quarter's own first column (0, 32, 64, 96)
             // B: K-major, head rows 16 B apart inside a core matrix, 8-row groups 128 B (SBO), dim chunks Q_LBO apart
-            umma_f16_ta(tmem_base + TM_S + 16 * qg, kp + 32 * (ks >> 1) + 8 * (ks & 1),
-                        umma_desc(q_addr + ks * 2 * Q_LBO, Q_LBO, 128), idesc_s, ks > 0 ? 1u : 0u);
+            umma_f16_ta_w(d_s, kp + 32 * (ks >> 1) + 8 * (ks & 1), q_lo + ks * ((2 * Q_LBO) >> 4), hi_128, idesc_s,
+                          ks > 0 ? 1u : 0u);
           }
           umma_commit(smem_u32(&sm.s_ready[qg]));   // also frees the rotated queries (the rotator waits on it too)
           ++qi;
@@ -667,6 +690,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
     if (lane == 0) {
       const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
       const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t v_lo0 = desc_lo(smem_u32(sm.v_tile[0]), 128), p_lo0 = desc_lo(smem_u32(sm.p_tile[0]), 128);
+      const uint32_t hi_2048 = desc_hi(2048), hi_0 = desc_hi(0), d_o = tmem_base + TM_O;
       int row_pv = row0;
       int c_row_lo = 0, c_row_hi = 0;   // tiles of the current batch row in this CTA: [c_row_lo, c_row_hi)
       for (int c = 0; c < n_stages; ++c) {
@@ -682,15 +707,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mma_decode_kernel(dkv_attn_args p
         if (!mbar_wait_thread(smem_u32(&sm.p_ready[grp]), (uint32_t)((c >> 1) & 1), abort_flag)) break;
         proxy_fence_async();   // V tile written by cp.async
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(sm.v_tile[vb]), p_addr = smem_u32(sm.p_tile[grp]);
+        const uint32_t v_lo = v_lo0 + (uint32_t)vb * (TILE_BYTES >> 4), p_lo = p_lo0 + (uint32_t)grp * ((ST_TOK * 16) >> 4);
+        const uint32_t acc0 = first ? 0u : 1u;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           // A = XV^T: MN-major, 16 tokens per step (256 B), token groups of 8 are 128 B apart (LBO), latent
           //     chunks 2048 B apart (SBO)
           // B = P:    MN-major, token groups of 8 are 128 B apart (LBO); the second group of 8 columns aliases
           //     the first (SBO 0): columns 8..15 of the result duplicate 0..7 and are never read
-          umma_f16(tmem_base + TM_O, umma_desc(v_addr + ks * 256, 128, 2048),
-                   umma_desc(p_addr + ks * 256, 128, 0), idesc_o, (ks > 0 || !first) ? 1u : 0u);
+          umma_f16_w(d_o, v_lo + ks * 16, hi_2048, p_lo + ks * 16, hi_0, idesc_o, ks > 0 ? 1u : acc0);
         }
         umma_commit(smem_u32(&sm.pv_done[grp]));
         umma_commit(smem_u32(&sm.v_free[vb]));

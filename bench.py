@@ -421,14 +421,17 @@ def tensor_pipe_probe(dev, tiles=100):
     from dynakv_b200.kernels._common import status_word, read_status
     lib = _lib.load()
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
-    cyc = torch.zeros(n_sm, dtype=torch.int64, device=dev)
+    cyc = torch.zeros(2 * n_sm, dtype=torch.int64, device=dev)
     out = {}
-    for name, mask in (("k_reconstruction", 1), ("scores", 2), ("latent_accumulation", 4), ("all_three", 7)):
+    for name, mask in (("k_reconstruction", 1), ("scores", 2), ("latent_accumulation", 4), ("all_three", 7),
+                       ("two_issuers_thread_1_2", 11)):
         for _ in range(2):
             _lib.check(lib.dkv_probe_tensor_pipe(mask, tiles, n_sm, cyc.data_ptr(), status_word(dev).data_ptr(),
                                                  _lib.stream_ptr(dev)), "dkv_probe_tensor_pipe")
         torch.cuda.synchronize()
-        out[name] = float(cyc.double().median().item()) / tiles
+        out[name] = float(cyc[:n_sm].double().median().item()) / tiles
+        if mask == 11:
+            out["two_issuers_thread_3"] = float(cyc[n_sm:].double().median().item()) / tiles
     out["status"] = read_status(dev)
     return {"cycles_per_tile": out, "tiles": tiles, "ctas": n_sm}
 

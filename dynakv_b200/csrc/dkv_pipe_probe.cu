@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(128) pipe_probe_kernel(long long* cycles, int3
   unsigned char* sB = pp_raw + 32768;     // basis
   unsigned char* sV = pp_raw + 65536;     // V operand tile
   unsigned char* sQ = pp_raw + 98304;     // rotated queries / P
-  unsigned long long* bar = reinterpret_cast<unsigned long long*>(pp_raw + 110592);
+  unsigned long long* bar = reinterpret_cast<unsigned long long*>(pp_raw + 110592);     // two barriers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pp_raw + 110592 + 64);
   const int tid = threadIdx.x, warp = tid >> 5;
   for (int e = tid; e < 110592 / 16; e += blockDim.x) reinterpret_cast<uint4*>(pp_raw)[e] = make_uint4(0, 0, 0, 0);
@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(128) pipe_probe_kernel(long long* cycles, int3
   }
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pp_smem(bar)));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pp_smem(bar + 1)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -86,6 +87,24 @@ __global__ void __launch_bounds__(128) pipe_probe_kernel(long long* cycles, int3
     if (!ok) set_status(status, DKV_ST_TIMEOUT);
     cycles[blockIdx.x] = t1 - t0;
   }
+  if (tid == 32 && (MASK & 8)) {
+    // product (3) from a second thread (another warp and SM sub-partition), as in the decode kernel
+    const uint32_t id_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+    const long long t0 = clock64();
+    for (int r = 0; r < tiles; ++r) {
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        pp_mma_ss(tb + 480, pp_desc(pp_smem(sV) + ks * 256, 128, 2048), pp_desc(pp_smem(sQ) + ks * 256, 128, 0), id_o, 1);
+    }
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pp_smem(bar + 1)) : "memory");
+    uint32_t ok = 0;
+    for (uint32_t it = 0; it < PROBE_SPIN && !ok; ++it)
+      asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0,1,0,p;\n}"
+                   : "=r"(ok) : "r"(pp_smem(bar + 1)), "r"(0u) : "memory");
+    const long long t1 = clock64();
+    if (!ok) set_status(status, DKV_ST_TIMEOUT);
+    cycles[gridDim.x + blockIdx.x] = t1 - t0;
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {
@@ -109,8 +128,10 @@ using namespace dkv;
 
 extern "C" int dkv_probe_tensor_pipe(int32_t products, int32_t tiles, int32_t n_cta, int64_t* cycles, int32_t* status,
                                      void* stream) {
-  DKV_REQUIRE(products >= 1 && products <= 7 && tiles >= 1 && tiles <= 100000 && n_cta >= 1 && n_cta <= 1024, DKV_E_ARG,
-              "dkv_probe_tensor_pipe: products is a mask of 1|2|4, tiles in 1..100000, n_cta in 1..1024");
+  DKV_REQUIRE(((products >= 1 && products <= 7) || products == 11) && tiles >= 1 && tiles <= 100000 && n_cta >= 1 &&
+                  n_cta <= 1024,
+              DKV_E_ARG, "dkv_probe_tensor_pipe: products is a mask of 1|2|4 (or 11 = 1|2 from one thread with product "
+                         "(3) from a second), tiles in 1..100000, n_cta in 1..1024");
   DKV_REQUIRE(cycles != nullptr, DKV_E_ARG, "dkv_probe_tensor_pipe: null output");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   long long* out = reinterpret_cast<long long*>(cycles);
@@ -122,6 +143,7 @@ extern "C" int dkv_probe_tensor_pipe(int32_t products, int32_t tiles, int32_t n_
     case 4: e = launch_probe<4>(n_cta, out, status, tiles, st); break;
     case 5: e = launch_probe<5>(n_cta, out, status, tiles, st); break;
     case 6: e = launch_probe<6>(n_cta, out, status, tiles, st); break;
+    case 11: e = launch_probe<11>(n_cta, out, status, tiles, st); break;
     default: e = launch_probe<7>(n_cta, out, status, tiles, st); break;
   }
   DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "dkv_probe_tensor_pipe: %s", cudaGetErrorString(e));

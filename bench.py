@@ -663,7 +663,7 @@ def cpu_reference(w, steps, warmup, max_seconds=25.0):
         xv = torch.from_numpy(O.decompress_gather(fv.float().numpy(), lv.numpy(), ov.numpy(), 128)).view(1, N_KV_HEADS, seq, 128)
         return case.q.float(), xk, xv, case.k_up.float(), case.v_up.float(), (lk > 0).view(1, N_KV_HEADS, seq)
 
-    def time_passes(inputs, theta, n, n_warm, budget):
+    def time_passes(inputs, theta, n, n_warm, limit_s):
         times, t_start = [], time.perf_counter()
         for i in range(n_warm + n):
             t0 = time.perf_counter()
@@ -671,7 +671,7 @@ def cpu_reference(w, steps, warmup, max_seconds=25.0):
             dt = time.perf_counter() - t0
             if i >= n_warm:
                 times.append(dt)
-            if time.perf_counter() - t_start > budget and len(times) >= 3:
+            if time.perf_counter() - t_start > limit_s and len(times) >= 3:
                 break
         return times
 

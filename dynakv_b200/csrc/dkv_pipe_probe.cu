@@ -29,6 +29,10 @@ __device__ __forceinline__ void pp_mma_ts(uint32_t d, uint32_t a, uint64_t db, u
                ::"r"(d), "r"(a), "l"(db), "r"(idesc), "r"(acc) : "memory");
 }
 
+__device__ __forceinline__ void pp_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 template <int MASK>
 __global__ void __launch_bounds__(128) pipe_probe_kernel(long long* cycles, int32_t* status, int tiles) {
   extern __shared__ __align__(1024) unsigned char pp_raw[];
@@ -36,7 +40,7 @@ __global__ void __launch_bounds__(128) pipe_probe_kernel(long long* cycles, int3
   unsigned char* sB = pp_raw + 32768;     // basis
   unsigned char* sV = pp_raw + 65536;     // V operand tile
   unsigned char* sQ = pp_raw + 98304;     // rotated queries / P
-  unsigned long long* bar = reinterpret_cast<unsigned long long*>(pp_raw + 110592);     // two barriers
+  unsigned long long* bar = reinterpret_cast<unsigned long long*>(pp_raw + 110592);     // six barriers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pp_raw + 110592 + 64);
   const int tid = threadIdx.x, warp = tid >> 5;
   for (int e = tid; e < 110592 / 16; e += blockDim.x) reinterpret_cast<uint4*>(pp_raw)[e] = make_uint4(0, 0, 0, 0);
@@ -48,6 +52,7 @@ __global__ void __launch_bounds__(128) pipe_probe_kernel(long long* cycles, int3
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pp_smem(bar)));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pp_smem(bar + 1)));
+    for (int i = 2; i < 6; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(pp_smem(bar + i)));   // per-chain commits, never waited on
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -65,17 +70,20 @@ __global__ void __launch_bounds__(128) pipe_probe_kernel(long long* cycles, int3
         for (int ks = 0; ks < 8; ++ks)
           pp_mma_ss(tb + 128 * (r % 3), pp_desc(pp_smem(sA) + ks * 4096, 2048, 128), pp_desc(pp_smem(sB) + ks * 4096, 2048, 128),
                     id_k, ks > 0);
+        if (MASK & 16) pp_commit(pp_smem(bar + 2));
       }
       if (MASK & 2) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           pp_mma_ts(tb + 448 + 16 * (r & 1), tb + 128 * ((r + 1) % 3) + 32 * (ks >> 1) + 8 * (ks & 1),
                     pp_desc(pp_smem(sQ) + ks * 2 * 272, 272, 128), id_s, ks > 0);
+        if (MASK & 16) pp_commit(pp_smem(bar + 3));
       }
       if (MASK & 4) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           pp_mma_ss(tb + 480, pp_desc(pp_smem(sV) + ks * 256, 128, 2048), pp_desc(pp_smem(sQ) + ks * 256, 128, 0), id_o, 1);
+        if (MASK & 16) { pp_commit(pp_smem(bar + 4)); pp_commit(pp_smem(bar + 5)); }
       }
     }
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pp_smem(bar)) : "memory");
@@ -128,7 +136,7 @@ using namespace dkv;
 
 extern "C" int dkv_probe_tensor_pipe(int32_t products, int32_t tiles, int32_t n_cta, int64_t* cycles, int32_t* status,
                                      void* stream) {
-  DKV_REQUIRE(((products >= 1 && products <= 7) || products == 11) && tiles >= 1 && tiles <= 100000 && n_cta >= 1 &&
+  DKV_REQUIRE(((products >= 1 && products <= 7) || products == 11 || products == 23) && tiles >= 1 && tiles <= 100000 && n_cta >= 1 &&
                   n_cta <= 1024,
               DKV_E_ARG, "dkv_probe_tensor_pipe: products is a mask of 1|2|4 (or 11 = 1|2 from one thread with product "
                          "(3) from a second), tiles in 1..100000, n_cta in 1..1024");
@@ -144,6 +152,7 @@ extern "C" int dkv_probe_tensor_pipe(int32_t products, int32_t tiles, int32_t n_
     case 5: e = launch_probe<5>(n_cta, out, status, tiles, st); break;
     case 6: e = launch_probe<6>(n_cta, out, status, tiles, st); break;
     case 11: e = launch_probe<11>(n_cta, out, status, tiles, st); break;
+    case 23: e = launch_probe<23>(n_cta, out, status, tiles, st); break;   // 7 with a commit behind every chain
     default: e = launch_probe<7>(n_cta, out, status, tiles, st); break;
   }
   DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "dkv_probe_tensor_pipe: %s", cudaGetErrorString(e));

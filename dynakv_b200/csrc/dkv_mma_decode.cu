@@ -128,27 +128,12 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // polling lane the other lanes' later shared-memory loads are not ordered behind the wait and can be scheduled
 // ahead of it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#ifdef DKV_POLL_LANE0
-  int ok = 0;
-  if ((threadIdx.x & 31) == 0) {
-    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
-      if (mbar_test(bar, parity)) { ok = 1; break; }
-      if ((it & 1023u) == 1023u && *abort_flag) break;
-      if (it + 1 == SPIN_LIMIT) *abort_flag = 1;
-    }
-  }
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  if (ok) (void)mbar_test(bar, parity);
-  __syncwarp();
-  return ok != 0;
-#else
   for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
     if (mbar_test(bar, parity)) return true;
     if ((it & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
-#endif
 }
 // Non-blocking probe of a barrier phase.
 __device__ __forceinline__ bool mbar_probe(uint32_t bar, uint32_t parity) {
@@ -185,20 +170,13 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 // tcgen05 (5th generation tensor core) helpers ---------------------------------------------------------
-// Shared-memory matrix descriptor, no swizzle: start address, leading and stride byte offsets in 16-byte
+// Shared-memory matrix descriptors are unswizzled: start address, leading and stride byte offsets in 16-byte
 // units, descriptor version 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
-         ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The same instructions with the operand descriptors passed as two 32-bit words: the issuer threads keep the words
-// of each ring slot ready and add the (compile-time) k-step offset to the low word, so that nothing but that add
-// stands between two tcgen05.mma of a product -- the descriptor arithmetic of umma_desc (shifts, masks and 64-bit
-// ors, ~15 dependent instructions per product step on a lone thread) was what an issue block waited on.
+// tcgen05.mma with the shared-memory operand descriptors passed as two 32-bit words (low = (address >> 4) |
+// (LBO >> 4) << 16, high = (SBO >> 4) | version bit 46): the issuer threads keep the words of each ring slot ready
+// and add the (compile-time) k-step offset to the low word, so that nothing but that add stands between two
+// tcgen05.mma of a product.  Building the 64-bit descriptor with shifts, masks and ors per step (~15 dependent
+// instructions on a lone thread) was what an issue block waited on.
 __device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo) { return ((addr >> 4) & 0x3FFFu) | (((lbo >> 4) & 0x3FFFu) << 16); }
 __device__ __forceinline__ uint32_t desc_hi(uint32_t sbo) { return ((sbo >> 4) & 0x3FFFu) | (1u << 14); }
 __device__ __forceinline__ void umma_f16_w(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
@@ -208,6 +186,7 @@ __device__ __forceinline__ void umma_f16_w(uint32_t tmem_d, uint32_t a_lo, uint3
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
       ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with the A operand in tensor memory (16-bit pairs packed in 32-bit cells, lane = row)
 __device__ __forceinline__ void umma_f16_ta_w(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                               uint32_t accumulate) {
   asm volatile(
@@ -221,11 +200,6 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// tcgen05.mma with the A operand in tensor memory (16-bit pairs packed in 32-bit cells, lane = row)
-__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Thread-per-lane tensor-memory access (32x32b shapes): thread i of the warp addresses lane (base lane + i),

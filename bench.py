@@ -424,7 +424,8 @@ def tensor_pipe_probe(dev, tiles=100):
     cyc = torch.zeros(2 * n_sm, dtype=torch.int64, device=dev)
     out = {}
     for name, mask in (("k_reconstruction", 1), ("scores", 2), ("latent_accumulation", 4), ("all_three", 7),
-                       ("all_three_commit_per_chain", 23), ("two_issuers_thread_1_2", 11)):
+                       ("all_three_commit_per_chain", 23), ("all_three_nonzero_operands", 39),
+                       ("two_issuers_nonzero_thread_1_2", 43), ("two_issuers_thread_1_2", 11)):
         for _ in range(2):
             _lib.check(lib.dkv_probe_tensor_pipe(mask, tiles, n_sm, cyc.data_ptr(), status_word(dev).data_ptr(),
                                                  _lib.stream_ptr(dev)), "dkv_probe_tensor_pipe")
@@ -432,6 +433,8 @@ def tensor_pipe_probe(dev, tiles=100):
         out[name] = float(cyc[:n_sm].double().median().item()) / tiles
         if mask == 11:
             out["two_issuers_thread_3"] = float(cyc[n_sm:].double().median().item()) / tiles
+        if mask == 43:
+            out["two_issuers_nonzero_thread_3"] = float(cyc[n_sm:].double().median().item()) / tiles
     out["status"] = read_status(dev)
     return {"cycles_per_tile": out, "tiles": tiles, "ctas": n_sm}
 

@@ -43,7 +43,16 @@ __global__ void __launch_bounds__(128) pipe_probe_kernel(long long* cycles, int3
   unsigned long long* bar = reinterpret_cast<unsigned long long*>(pp_raw + 110592);     // six barriers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pp_raw + 110592 + 64);
   const int tid = threadIdx.x, warp = tid >> 5;
-  for (int e = tid; e < 110592 / 16; e += blockDim.x) reinterpret_cast<uint4*>(pp_raw)[e] = make_uint4(0, 0, 0, 0);
+  for (int e = tid; e < 110592 / 16; e += blockDim.x) {
+    // zero operands, or (mask bit 32) a non-trivial bit pattern: small bf16 values of both signs
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (MASK & 32) {
+      const uint32_t h = (uint32_t)e * 2654435761u;
+      v = make_uint4(0x3c003b00u ^ (h & 0x80ff80ffu), 0x3a803c80u ^ ((h >> 3) & 0x80ff80ffu), 0x3b403bc0u ^ ((h >> 7) & 0x80ff80ffu),
+                     0x3c403a40u ^ ((h >> 11) & 0x80ff80ffu));
+    }
+    reinterpret_cast<uint4*>(pp_raw)[e] = v;
+  }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pp_smem(tmem_slot)), "r"(512));
@@ -136,7 +145,7 @@ using namespace dkv;
 
 extern "C" int dkv_probe_tensor_pipe(int32_t products, int32_t tiles, int32_t n_cta, int64_t* cycles, int32_t* status,
                                      void* stream) {
-  DKV_REQUIRE(((products >= 1 && products <= 7) || products == 11 || products == 23) && tiles >= 1 && tiles <= 100000 && n_cta >= 1 &&
+  DKV_REQUIRE(((products >= 1 && products <= 7) || products == 11 || products == 23 || products == 39 || products == 43) && tiles >= 1 && tiles <= 100000 && n_cta >= 1 &&
                   n_cta <= 1024,
               DKV_E_ARG, "dkv_probe_tensor_pipe: products is a mask of 1|2|4 (or 11 = 1|2 from one thread with product "
                          "(3) from a second), tiles in 1..100000, n_cta in 1..1024");
@@ -153,6 +162,8 @@ extern "C" int dkv_probe_tensor_pipe(int32_t products, int32_t tiles, int32_t n_
     case 6: e = launch_probe<6>(n_cta, out, status, tiles, st); break;
     case 11: e = launch_probe<11>(n_cta, out, status, tiles, st); break;
     case 23: e = launch_probe<23>(n_cta, out, status, tiles, st); break;   // 7 with a commit behind every chain
+    case 39: e = launch_probe<39>(n_cta, out, status, tiles, st); break;   // 7 over non-zero operands
+    case 43: e = launch_probe<43>(n_cta, out, status, tiles, st); break;   // 11 over non-zero operands
     default: e = launch_probe<7>(n_cta, out, status, tiles, st); break;
   }
   DKV_REQUIRE(e == cudaSuccess, DKV_E_CUDA, "dkv_probe_tensor_pipe: %s", cudaGetErrorString(e));

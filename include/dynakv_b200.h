@@ -207,7 +207,8 @@ int dkv_pack_bulk(const dkv_pack_args* a);
  * else running on the SM.  `products` is a mask: 1 = K reconstruction (8 x M128 N128 K16), 2 = scores (8 x M128 N16
  * K16, A in tensor memory), 4 = latent accumulation (8 x M128 N16 K16); 11 = products 1 and 2 from one thread with
  * product 4's chain issued concurrently by a thread of another warp, as the decode kernel does; 23 = all three from
- * one thread with a tcgen05.commit behind every chain (the kernel's four commits per tile).  Launches n_cta
+ * one thread with a tcgen05.commit behind every chain (the kernel's four commits per tile); 39 and 43 = 7 and 11
+ * over non-zero operands.  Launches n_cta
  * CTAs (one per SM when n_cta <= the SM count) of `tiles` tiles each and writes cycles[c] = elapsed clock64 of CTA c
  * for all its tiles (and, for 11, cycles[n_cta + c] for the second thread: `cycles` holds 2 * n_cta values).
  * The wait for the products is bounded; DKV_ST_TIMEOUT is set in *status when it runs out. */

@@ -115,3 +115,38 @@ def test_balanced_sequence_partition_covers_every_sequence_and_balances_tokens()
         assert max(loads) - min(loads) <= max(lengths)          # longest-first greedy bound
         assert max(loads) <= 1.25 * sum(lengths) / world or world == 1 or max(lengths) > sum(lengths) / world
     assert sharding.balanced_sequence_partition([5, 5], 4) == [[0], [1], [], []]
+
+
+def test_ctypes_mirrors_have_the_c_compilers_layout(tmp_path):
+    """Every struct of include/dynakv_b200.h, field by field: size and offsets as gcc lays them out against the
+    ctypes mirror in dynakv_b200/_lib.py (same field names, same order)."""
+    import os
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    pairs = {"dkv_side": _lib.Side, "dkv_attn_args": _lib.AttnArgs, "dkv_append_args": _lib.AppendArgs,
+             "dkv_pack_args": _lib.PackArgs, "dkv_project_args": _lib.ProjectArgs, "dkv_gate_args": _lib.GateArgs}
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "dynakv_b200.h"', "int main(void) {"]
+    for cname, cls in pairs.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for fname, _ in cls._fields_:
+            lines.append(f'  printf("{cname} {fname} %zu\\n", offsetof({cname}, {fname}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    inc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    subprocess.run([gcc, "-std=c99", "-I", inc, str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    seen = 0
+    for line in out.splitlines():
+        cname, what, value = line.split()
+        cls = pairs[cname]
+        if what == "size":
+            assert ctypes.sizeof(cls) == int(value), (cname, ctypes.sizeof(cls), value)
+        else:
+            assert getattr(cls, what).offset == int(value), (cname, what)
+        seen += 1
+    assert seen == sum(len(c._fields_) + 1 for c in pairs.values())

@@ -22,7 +22,7 @@ _DTYPES = {torch.float32: DKV_F32, torch.float16: DKV_F16, torch.bfloat16: DKV_B
 EXPORTS = (
     "dkv_version", "dkv_last_error", "dkv_fused_decode", "dkv_split_workspace_bytes", "dkv_split_decode",
     "dkv_split_combine", "dkv_two_stage_decode", "dkv_two_stage_decode_noalloc", "dkv_scores", "dkv_softmax_v", "dkv_append_decode",
-    "dkv_pack_bulk", "dkv_decompress", "dkv_gate_lengths", "dkv_gate_workspace_bytes", "dkv_project_bulk", "dkv_probe_tensor_pipe",
+    "dkv_pack_bulk", "dkv_decompress", "dkv_gate_lengths", "dkv_gate_workspace_bytes", "dkv_gate_lengths_pair", "dkv_project_bulk", "dkv_probe_tensor_pipe",
 )
 
 
@@ -128,6 +128,8 @@ def load() -> C.CDLL:
     lib.dkv_gate_lengths.restype = C.c_int
     lib.dkv_gate_workspace_bytes.argtypes = [C.POINTER(GateArgs)]
     lib.dkv_gate_workspace_bytes.restype = C.c_size_t
+    lib.dkv_gate_lengths_pair.argtypes = [C.POINTER(GateArgs), C.POINTER(GateArgs)]
+    lib.dkv_gate_lengths_pair.restype = C.c_int
     lib.dkv_project_bulk.argtypes = [C.POINTER(ProjectArgs)]
     lib.dkv_project_bulk.restype = C.c_int
     lib.dkv_probe_tensor_pipe.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]

@@ -84,43 +84,13 @@ __global__ void __launch_bounds__(GATE_TILE) gate_logits_kernel(dkv_gate_args p,
   }
 }
 
-// one warp per row: logits = b + sum of the chunk partials, softmax, running sum, count
+// The rest of a row, one warp per row, from its logits (in lg, shared memory) and this lane's partial maximum:
+// softmax, running sum, count, optional masked copy.  Shared by the two-kernel path and the single-kernel path for
+// narrow rows, so that both do the same arithmetic in the same order.
 template <typename T>
-__global__ void __launch_bounds__(256) gate_count_kernel(dkv_gate_args p, int n_chunks) {
-  __shared__ float lg_s[8][GATE_MAX_DIM];
-  const int d = p.dim, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row = blockIdx.x * 8 + warp;
-  if (row >= p.n_rows) return;
-  const T* b = reinterpret_cast<const T*>(p.b);
-  const bool native = p.native_rounding != 0 && sizeof(T) == 2;
-  const float thr = native ? to_f32(from_f32<T>(p.threshold)) : p.threshold;   // the comparison converts the scalar
-  const float* part = reinterpret_cast<const float*>(p.workspace);
-  float* lg = lg_s[warp];
-  float mx = -INFINITY;
-  const size_t cstride = (size_t)p.n_rows * d;   // between the partials of consecutive chunks
-  for (int jb = lane; jb < d; jb += 32 * 4) {
-    // four columns at a time, all their partials loaded before the (fixed-order) additions
-    float pv[4][8];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = jb + 32 * u;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) pv[u][c] = (j < d && c < n_chunks) ? part[c * cstride + (size_t)row * d + j] : 0.f;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = jb + 32 * u;
-      if (j < d) {
-        float v = 0.f;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) v += pv[u][c];
-        v += to_f32(b[j]);
-        if (native) v = to_f32(from_f32<T>(v));   // addmm writes the logits in the storage type
-        lg[j] = v;
-        mx = fmaxf(mx, v);
-      }
-    }
-  }
+__device__ __forceinline__ void gate_finish_row(const dkv_gate_args& p, int row, float* lg, float mx, int lane, bool native,
+                                                float thr) {
+  const int d = p.dim;
   mx = warp_max(mx);
   float z = 0.f;
   for (int j = lane; j < d; j += 32) {
@@ -164,6 +134,103 @@ __global__ void __launch_bounds__(256) gate_count_kernel(dkv_gate_args p, int n_
     const T* xr = x + (size_t)row * p.x_stride;
     for (int i = lane; i < d; i += 32) out[i] = i < cnt ? xr[i] : from_f32<T>(0.f);
   }
+}
+
+// one warp per row: logits = b + sum of the chunk partials, softmax, running sum, count
+template <typename T>
+__global__ void __launch_bounds__(256) gate_count_kernel(dkv_gate_args p, int n_chunks) {
+  __shared__ float lg_s[8][GATE_MAX_DIM];
+  const int d = p.dim, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= p.n_rows) return;
+  const T* b = reinterpret_cast<const T*>(p.b);
+  const bool native = p.native_rounding != 0 && sizeof(T) == 2;
+  const float thr = native ? to_f32(from_f32<T>(p.threshold)) : p.threshold;   // the comparison converts the scalar
+  const float* part = reinterpret_cast<const float*>(p.workspace);
+  float* lg = lg_s[warp];
+  float mx = -INFINITY;
+  const size_t cstride = (size_t)p.n_rows * d;   // between the partials of consecutive chunks
+  for (int jb = lane; jb < d; jb += 32 * 4) {
+    // four columns at a time, all their partials loaded before the (fixed-order) additions
+    float pv[4][8];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = jb + 32 * u;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) pv[u][c] = (j < d && c < n_chunks) ? part[c * cstride + (size_t)row * d + j] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = jb + 32 * u;
+      if (j < d) {
+        float v = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v += pv[u][c];
+        v += to_f32(b[j]);
+        if (native) v = to_f32(from_f32<T>(v));   // addmm writes the logits in the storage type
+        lg[j] = v;
+        mx = fmaxf(mx, v);
+      }
+    }
+  }
+  gate_finish_row<T>(p, row, lg, mx, lane, native, thr);
+}
+
+// Narrow rows (dim <= 128, the per-head decode shape), K and V sides in one launch: blockIdx.y picks the side, a
+// CTA takes 8 rows; the logits go straight to shared memory (same fp32 sum, i ascending, as the two-kernel path
+// with one reduction chunk), then one warp per row finishes as above.
+template <typename T>
+__global__ void __launch_bounds__(256) gate_small_kernel(dkv_gate_args pk, dkv_gate_args pv) {
+  __shared__ float xs[8][GATE_TILE];
+  __shared__ float lg_s[8][GATE_TILE];
+  const dkv_gate_args& p = blockIdx.y ? pv : pk;
+  const int d = p.dim, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row0 = blockIdx.x * 8;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* w = reinterpret_cast<const T*>(p.w);
+  const T* b = reinterpret_cast<const T*>(p.b);
+  const bool native = p.native_rounding != 0 && sizeof(T) == 2;
+  const float thr = native ? to_f32(from_f32<T>(p.threshold)) : p.threshold;
+  for (int e = tid; e < 8 * d; e += 256) {
+    const int r = e / d, i = e - r * d;
+    xs[r][i] = (row0 + r < p.n_rows) ? to_f32(x[(size_t)(row0 + r) * p.x_stride + i]) : 0.f;
+  }
+  __syncthreads();
+  {
+    const int col = tid & (GATE_TILE - 1), rq = (tid >> 7) * 4;   // four rows per thread
+    if (col < d) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      int i = 0;
+      for (; i + 8 <= d; i += 8) {
+        float wv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) wv[u] = to_f32(w[(size_t)(i + u) * d + col]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) acc[r] = fmaf(xs[rq + r][i + u], wv[u], acc[r]);
+      }
+      for (; i < d; ++i) {
+        const float wv = to_f32(w[(size_t)i * d + col]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[r] = fmaf(xs[rq + r][i], wv, acc[r]);
+      }
+      const float bias = to_f32(b[col]);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        float v = acc[r] + bias;
+        if (native) v = to_f32(from_f32<T>(v));   // addmm writes the logits in the storage type
+        lg_s[rq + r][col] = v;
+      }
+    }
+  }
+  __syncthreads();
+  const int row = row0 + warp;
+  if (row >= p.n_rows) return;
+  float* lg = lg_s[warp];
+  float mx = -INFINITY;
+  for (int j = lane; j < d; j += 32) mx = fmaxf(mx, lg[j]);
+  gate_finish_row<T>(p, row, lg, mx, lane, native, thr);
 }
 
 static int gate_chunks(const dkv_gate_args* a) {
@@ -212,6 +279,30 @@ extern "C" int dkv_gate_lengths(const dkv_gate_args* a) {
   else if (a->dtype == DKV_F16) LAUNCH(__half);
   else LAUNCH(__nv_bfloat16);
 #undef LAUNCH
+  DKV_CHECK_LAUNCH();
+  return DKV_OK;
+}
+
+extern "C" int dkv_gate_lengths_pair(const dkv_gate_args* k, const dkv_gate_args* v) {
+  using namespace dkv;
+  DKV_REQUIRE(k != nullptr && v != nullptr, DKV_E_ARG, "dkv_gate_lengths_pair: null args");
+  DKV_REQUIRE(k->dtype == v->dtype && k->dim == v->dim && k->n_rows == v->n_rows && k->stream == v->stream, DKV_E_ARG,
+              "dkv_gate_lengths_pair: the two sides must agree in dtype, dim, rows and stream");
+  DKV_REQUIRE(k->dtype >= DKV_F32 && k->dtype <= DKV_BF16, DKV_E_ARG, "dkv_gate_lengths_pair: bad dtype %d", k->dtype);
+  DKV_REQUIRE(k->n_rows >= 0 && k->dim >= 1 && k->dim <= GATE_TILE, DKV_E_LIMIT,
+              "dkv_gate_lengths_pair: dim must be in 1..%d (wider rows: dkv_gate_lengths per side)", GATE_TILE);
+  for (const dkv_gate_args* a : {k, v}) {
+    DKV_REQUIRE(a->x && a->w && a->b && a->lengths, DKV_E_ARG, "dkv_gate_lengths_pair: null input");
+    DKV_REQUIRE(a->x_stride >= a->dim && (!a->masked || a->masked_stride >= a->dim), DKV_E_ARG,
+                "dkv_gate_lengths_pair: row strides must be at least dim");
+  }
+  if (k->n_rows == 0) return DKV_OK;
+  DKV_REQUIRE((k->n_rows + 7) / 8 <= 2147483647 / 8, DKV_E_LIMIT, "dkv_gate_lengths_pair: too many rows");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(k->stream);
+  const dim3 grid((k->n_rows + 7) / 8, 2);
+  if (k->dtype == DKV_F32) gate_small_kernel<float><<<grid, 256, 0, st>>>(*k, *v);
+  else if (k->dtype == DKV_F16) gate_small_kernel<__half><<<grid, 256, 0, st>>>(*k, *v);
+  else gate_small_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(*k, *v);
   DKV_CHECK_LAUNCH();
   return DKV_OK;
 }

@@ -112,6 +112,40 @@ def gate_lengths(states: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
     return (masked.reshape(*lead, d) if return_masked else None), lengths.reshape(lead)
 
 
+def gate_lengths_pair(k_rows: torch.Tensor, Wk: torch.Tensor, bk: torch.Tensor, v_rows: torch.Tensor, Wv: torch.Tensor,
+                      bv: torch.Tensor, low_rank: int, out_len_k: torch.Tensor, out_len_v: torch.Tensor,
+                      threshold: float = 0.1, len_multiple: int = 1, native_rounding: bool = True) -> None:
+    """The cutoffs of the K rows and of the V rows in one launch, for rows of at most 128 coefficients (the decode
+    shape of the per-head layout): the lengths ``gate_lengths`` gives for each side, written into the caller's int32
+    tensors.  Nothing is allocated."""
+    if not k_rows.is_cuda:
+        raise RuntimeError("dynakv_b200 has no CPU path: the gate needs CUDA tensors")
+    d = k_rows.shape[-1]
+    if d > 128 or v_rows.shape != k_rows.shape:
+        raise ValueError("gate_lengths_pair takes K and V rows of one shape with at most 128 coefficients")
+    args = []
+    keep = []
+    for rows, w, b, out in ((k_rows, Wk, bk, out_len_k), (v_rows, Wv, bv, out_len_v)):
+        if w.shape != (d, d) or b.numel() != d or w.dtype != rows.dtype or b.dtype != rows.dtype:
+            raise ValueError(f"gate weight must be [{d}, {d}] and bias [{d}] in the rows' dtype")
+        x = rows.reshape(-1, d)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        wc, bc = w.contiguous(), b.reshape(-1).contiguous()
+        if out.dtype != torch.int32 or out.numel() != x.shape[0] or not out.is_contiguous():
+            raise ValueError("the length outputs must be contiguous int32 tensors with one entry per row")
+        a = _lib.GateArgs()
+        a.dtype, a.n_rows, a.dim, a.low_rank, a.threshold = _lib.dtype_code(rows.dtype), x.shape[0], d, int(low_rank), threshold
+        a.x, a.x_stride, a.w, a.b = x.data_ptr(), x.stride(0), wc.data_ptr(), bc.data_ptr()
+        a.lengths, a.masked, a.masked_stride = out.data_ptr(), None, 0
+        a.len_multiple, a.native_rounding = int(len_multiple), int(bool(native_rounding))
+        a.stream = _lib.stream_ptr(rows.device)
+        args.append(a)
+        keep += [x, wc, bc]
+    _lib.check(_lib.load().dkv_gate_lengths_pair(C.byref(args[0]), C.byref(args[1])), "dkv_gate_lengths_pair")
+    del keep
+
+
 def kv_process_fused(key_states: torch.Tensor, value_states: torch.Tensor, Wk, bk, Wv, bv, low_rank: int,
                      len_multiple: int = 1):
     """Drop-in for the reference module method of the same name (kernels/compressed_attention.py:84-119):
@@ -158,8 +192,12 @@ class CompressedDecodeLayer:
         if self.gate is not None:
             Wk, bk, Wv, bv = self.gate
             R = new_k.shape[-1]
-            gate_lengths(new_k.view(-1, R), Wk, bk, R, return_masked=False, len_multiple=cache.len_multiple, out_lengths=len_k)
-            gate_lengths(new_v.view(-1, R), Wv, bv, R, return_masked=False, len_multiple=cache.len_multiple, out_lengths=len_v)
+            if R <= 128:      # both sides in one launch
+                gate_lengths_pair(new_k.view(-1, R), Wk, bk, new_v.view(-1, R), Wv, bv, R, len_k, len_v,
+                                  len_multiple=cache.len_multiple)
+            else:
+                gate_lengths(new_k.view(-1, R), Wk, bk, R, return_masked=False, len_multiple=cache.len_multiple, out_lengths=len_k)
+                gate_lengths(new_v.view(-1, R), Wv, bv, R, return_masked=False, len_multiple=cache.len_multiple, out_lengths=len_v)
         ck, cv = cache.key_cache_sp[self.layer_idx], cache.value_cache_sp[self.layer_idx]
         a = _lib.AppendArgs()
         a.dtype = _lib.dtype_code(new_k.dtype)
@@ -227,7 +265,7 @@ class DecodeGraph:
         self._has_long = reach >= switch
         self._switch = switch
         self.kernel_launches_per_step = L * (1 + (1 if self._has_short else 0) + (2 if self._has_long else 0)) + \
-            4 * sum(1 for l in self.layers if l.gate is not None)
+            sum(1 for l in self.layers if l.gate is not None)     # the gate of both sides is one launch
         for l in self.layers:       # size the gate's scratch and the append's tickets before any capture
             l.prepare(batch, self.device)
             if l.gate is not None:

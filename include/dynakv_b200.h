@@ -272,6 +272,12 @@ typedef struct dkv_gate_args {
 size_t dkv_gate_workspace_bytes(const dkv_gate_args* args);
 int dkv_gate_lengths(const dkv_gate_args* args);
 
+/* The gate for narrow rows (dim <= 128: one row per (sequence, KV head), the decode shape of the per-head layout),
+ * K and V sides in ONE launch and without a workspace: same arithmetic, in the same order, as dkv_gate_lengths on
+ * each side (kv_process_fused computes both sides in one call too, compressed_attention.py:92-114).  The two
+ * argument blocks must agree in dtype, dim, n_rows and stream; workspace fields are ignored. */
+int dkv_gate_lengths_pair(const dkv_gate_args* k, const dkv_gate_args* v);
+
 /* ---- misc -------------------------------------------------------------- */
 int dkv_version(void);
 const char* dkv_last_error(void);

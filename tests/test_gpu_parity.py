@@ -296,6 +296,28 @@ def test_bulk_pack_that_does_not_fit_records_empty_tokens_and_keeps_the_pointer(
     assert bool((ck[1] == -7).all()) and ck[3].tolist() == [S * 8, 0]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "fp16", "fp32"])
+@pytest.mark.parametrize("d", [128, 96])
+def test_gate_of_both_sides_in_one_launch_gives_the_lengths_of_the_two_kernel_path(dtype, d):
+    from dynakv_b200.kernels.compressed_attention import gate_lengths, gate_lengths_pair
+    gen = torch.Generator().manual_seed(77)
+    n = 37
+    xk = (torch.randn(n, d, generator=gen) * 2).to(dtype).to(DEV)
+    xv = (torch.randn(n, d, generator=gen) * 2).to(dtype).to(DEV)
+    Wk = (torch.randn(d, d, generator=gen) * 0.3).to(dtype).to(DEV)
+    Wv = (torch.randn(d, d, generator=gen) * 0.3).to(dtype).to(DEV)
+    bk = torch.randn(d, generator=gen).to(dtype).to(DEV)
+    bv = torch.randn(d, generator=gen).to(dtype).to(DEV)
+    for mult in (1, 8):
+        lk = torch.empty(n, dtype=torch.int32, device=DEV)
+        lv = torch.empty(n, dtype=torch.int32, device=DEV)
+        gate_lengths_pair(xk, Wk, bk, xv, Wv, bv, d, lk, lv, len_multiple=mult)
+        _, want_k = gate_lengths(xk, Wk, bk, d, return_masked=False, len_multiple=mult)
+        _, want_v = gate_lengths(xv, Wv, bv, d, return_masked=False, len_multiple=mult)
+        assert torch.equal(lk, want_k) and torch.equal(lv, want_v)
+        assert int(lk.min()) >= 1 and len(set(lk.tolist())) > 3     # a spread of cutoffs, not one value
+
+
 # ------------------------------------------------------------------ benchmark-shaped configurations
 def _case_args(case):
     fk, fv, lk, lv, ok, ov = case.views()

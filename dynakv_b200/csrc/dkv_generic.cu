@@ -129,13 +129,21 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
           for (int n = 0; n < 2; ++n)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
-        for (int r0 = 0; r0 < rmax; r0 += GRC) {
-          for (int e = tid; e < GTT * GRC; e += GTHREADS) {
-            const int t = e / GRC, rr = e - t * GRC, r = r0 + rr;
-            xs[t][rr] = (r < lenk_s[t]) ? kflat[(size_t)offk_s[t] + r] : from_f32<T>(0.f);
+        // The chunk after the one being multiplied is already on its way from global memory into registers (8
+        // coefficients and 4 basis pieces per thread), so a step costs max(load, products), not their sum.
+        constexpr int XPT = GTT * GRC / GTHREADS;            // x elements per thread per chunk (8)
+        constexpr int BPT = GRC * (GD / 8) / GTHREADS;       // 16-byte basis pieces per thread per chunk (4)
+        T xr[XPT];
+        uint4 br[BPT];
+        auto fetch = [&](int r0) {
+#pragma unroll
+          for (int u = 0; u < XPT; ++u) {
+            const int e = tid + u * GTHREADS, t = e / GRC, r = r0 + (e - t * GRC);
+            xr[u] = (r < lenk_s[t]) ? kflat[(size_t)offk_s[t] + r] : from_f32<T>(0.f);
           }
-          for (int e = tid; e < GRC * (GD / 8); e += GTHREADS) {
-            const int rr = e >> 4, c = e & 15, r = r0 + rr;
+#pragma unroll
+          for (int u = 0; u < BPT; ++u) {
+            const int e = tid + u * GTHREADS, rr = e >> 4, c = e & 15, r = r0 + rr;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (r < R) {
               if (vec) {
@@ -147,9 +155,23 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
                 v = *reinterpret_cast<const uint4*>(tmp);
               }
             }
-            *reinterpret_cast<uint4*>(&bs[rr][8 * c]) = v;
+            br[u] = v;
+          }
+        };
+        if (rmax > 0) fetch(0);
+        for (int r0 = 0; r0 < rmax; r0 += GRC) {
+#pragma unroll
+          for (int u = 0; u < XPT; ++u) {
+            const int e = tid + u * GTHREADS, t = e / GRC;
+            xs[t][e - t * GRC] = xr[u];
+          }
+#pragma unroll
+          for (int u = 0; u < BPT; ++u) {
+            const int e = tid + u * GTHREADS;
+            *reinterpret_cast<uint4*>(&bs[e >> 4][8 * (e & 15)]) = br[u];
           }
           __syncthreads();
+          if (r0 + GRC < rmax) fetch(r0 + GRC);
           const int ksteps = (min(GRC, rmax - r0) + 15) >> 4;
           for (int ks = 0; ks < ksteps; ++ks) {
             uint32_t af[2][4], bf[4];

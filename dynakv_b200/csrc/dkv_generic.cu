@@ -73,6 +73,13 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
     const T* qp = reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_stride_b + (size_t)h * p.q_stride_h;
     q_s[tid] = to_f32(qp[tid]);
   }
+  // rotation frequencies of this lane's two pairs (dims lane, lane + 64 and lane + 32, lane + 96) and the rotation by
+  // 8 positions (the token stride of a warp)
+  const float fa = expf(-((float)(2 * lane) / (float)GD) * log_theta);
+  const float fb = expf(-((float)(2 * (lane + 32)) / (float)GD) * log_theta);
+  float s8a, c8a, s8b, c8b;
+  sincosf(8.f * fa, &s8a, &c8a);
+  sincosf(8.f * fb, &s8b, &c8b);
   float m_run = -INFINITY;
   float acc_lat[4] = {0.f, 0.f, 0.f, 0.f};
   if (tid == 0) l_s = 0.f;
@@ -235,7 +242,10 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
       }
       __syncthreads();
 
-      // ---- optional RMSNorm, RoPE, q.k : one warp per token ----
+      // ---- optional RMSNorm, RoPE, q.k : one warp per token (tokens warp, warp + 8, ...) ----
+      // 16-bit types: exact sincos for the warp's first token of the tile, then a rotation by 8 positions per step
+      // (three steps; the 16-bit tolerance is 2e-2).  fp32 keeps one exact sincos per token, the reference's arithmetic.
+      float sa = 0.f, ca = 1.f, sb = 0.f, cb = 1.f;
       for (int t = warp; t < GTT; t += GTHREADS / 32) {
         const int s = t0 + t;
         float k0a = k_s[t][lane], k0b = k_s[t][lane + 32];            // dims j = lane, lane+32
@@ -248,11 +258,14 @@ generic_decode_kernel(dkv_attn_args p, const T* __restrict__ scores_in, int64_t 
           k1a = p.k_norm_weight[lane + 64] * (k1a * rs);
           k1b = p.k_norm_weight[lane + 96] * (k1b * rs);
         }
-        const float fa = expf(-((float)(2 * lane) / (float)GD) * log_theta);
-        const float fb = expf(-((float)(2 * (lane + 32)) / (float)GD) * log_theta);
-        float sa, ca, sb, cb;
-        sincosf((float)s * fa, &sa, &ca);
-        sincosf((float)s * fb, &sb, &cb);
+        if (sizeof(T) != 2 || t == warp) {
+          sincosf((float)s * fa, &sa, &ca);
+          sincosf((float)s * fb, &sb, &cb);
+        } else {
+          const float ca2 = ca * c8a - sa * s8a, sa2 = sa * c8a + ca * s8a;
+          const float cb2 = cb * c8b - sb * s8b, sb2 = sb * c8b + cb * s8b;
+          ca = ca2; sa = sa2; cb = cb2; sb = sb2;
+        }
         float part = q_s[lane] * (k0a * ca - k1a * sa) + q_s[lane + 64] * (k1a * ca + k0a * sa) +
                      q_s[lane + 32] * (k0b * cb - k1b * sb) + q_s[lane + 96] * (k1b * cb + k0b * sb);
         part = warp_sum(part);
@@ -367,7 +380,7 @@ template <typename T>
 __global__ void __launch_bounds__(GTHREADS) generic_combine_kernel(dkv_attn_args p, int n_split) {
   __shared__ float lat_s[1024];
   __shared__ float w_s[64];
-  __shared__ float half_s[GD];
+  __shared__ float red_s[16][GD];
   __shared__ float L_s;
   const int tid = threadIdx.x, h = blockIdx.y, Hq = p.n_q_heads, R = p.rank;
   const int b = p.batch_index ? p.batch_index[blockIdx.x] : blockIdx.x;
@@ -399,24 +412,48 @@ __global__ void __launch_bounds__(GTHREADS) generic_combine_kernel(dkv_attn_args
     lat_s[r] = v * inv;
   }
   __syncthreads();
+  // projection through Bv: thread (rg, dg) takes latent rows rg, rg + 16, ... and the 8 output dims 8 dg..8 dg + 7
+  // (one 16-byte load per row, eight rows in flight); the 16 row groups are added up through shared memory
   const T* vup = reinterpret_cast<const T*>(p.v_up) + (size_t)g * R * GD;
-  const int d = tid & (GD - 1), th = tid >> 7;
-  const int r_half = (R + 1) / 2, r_lo = th * r_half, r_hi = min(R, r_lo + r_half);
-  float o = 0.f;
-  for (int r = r_lo; r < r_hi; ++r) o = fmaf(lat_s[r], to_f32(vup[(size_t)r * GD + d]), o);
-  if (th == 1) half_s[d] = o;
+  const int dg = tid & 15, rg = tid >> 4;
+  const bool vec = (reinterpret_cast<uintptr_t>(p.v_up) & 15) == 0 && sizeof(T) == 2;
+  float acc8[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc8[e] = 0.f;
+  if (vec) {
+#pragma unroll 8
+    for (int r = rg; r < R; r += 16) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(vup + (size_t)r * GD) + dg);
+      const T* vp = reinterpret_cast<const T*>(&v);
+      const float lr = lat_s[r];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc8[e] = fmaf(lr, to_f32(vp[e]), acc8[e]);
+    }
+  } else {
+#pragma unroll 4
+    for (int r = rg; r < R; r += 16) {
+      const float lr = lat_s[r];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc8[e] = fmaf(lr, to_f32(vup[(size_t)r * GD + 8 * dg + e]), acc8[e]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red_s[rg][8 * dg + e] = acc8[e];
   __syncthreads();
-  if (th == 0) {
+  if (tid < GD) {
+    float o = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) o += red_s[k][tid];
     T* op = reinterpret_cast<T*>(p.out) + (size_t)b * p.out_stride_b + (size_t)h * p.out_stride_h;
-    op[d] = from_f32<T>(o + half_s[d]);
+    op[tid] = from_f32<T>(o);
   }
 }
 
-// Slices of the token axis for the two-stage entry on caches that take this path: at least 256 tokens each, at most 64.
+// Slices of the token axis for the two-stage entry on caches that take this path: at least 128 tokens each, at most 64.
 static int generic_split_tokens(const dkv_attn_args* a) {
   int t = (a->seq_len + 63) / 64;
   t = (t + GTT - 1) / GTT * GTT;
-  return t < 256 ? 256 : t;
+  return t < 128 ? 128 : t;
 }
 static int generic_n_split(const dkv_attn_args* a) {
   const int t = generic_split_tokens(a);
